@@ -34,6 +34,7 @@ SOURCES = [
     "window_attention.cu",
     "nomanex.cu",
     "zinavik.cu",
+    "mulenex.cu",
     "model_registry.cc",
     "abi_ops.cu",
     "engine.cu",

@@ -10,6 +10,10 @@
 // elementwise kernel, in fp32 with the accurate library functions; q, k and alpha of a group of tokens are staged in
 // shared memory once per CTA.  The state lives in HBM between steps ([slot][head][dim][vdim] fp32) and is read and
 // written once per step.
+//
+// The same scan serves recurrences whose gates are scalars per (token, head) (tok_decay / tok_kscale), among them the
+// matrix memory with exponential gating (mLSTM): its gates come from `mlstm_gates`, its normaliser n_t = d n + s k rides
+// along as one more value column of ones, and `recurrent_out_gate` divides by max(|n . q|, exp(-m)) before the norm.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -52,13 +56,17 @@ __global__ void gla_decay_kernel(float* z, const float* bias, int HD, float inv_
 // from shared memory then feeds twice the arithmetic).  Threads of a warp share one row slice (part = thread / tcols), so a
 // shared-memory read of q, k or alpha is one broadcast; the P partial outputs of a column meet in shared memory and are
 // summed by the pass that writes the round's outputs.
-// CD: one constant decay per head (GlaArgs::head_decay): no decay row is staged or read, the constant sits in a register.
-template <typename T, int NC, bool CD>
+// MODE 0: learned per-channel decays, staged as a third row.  MODE 1: one constant decay per head (GlaArgs::head_decay): no
+// decay row is staged or read, the constant sits in a register.  MODE 2: one decay and one key scale per (token, head)
+// (GlaArgs::tok_decay / tok_kscale): the decays of a round's tokens sit in shared memory as G scalars, the key is scaled
+// as it is staged.  With GlaArgs::ones_col the state has one more value column whose v is 1 for every token.
+template <typename T, int NC, int MODE>
 __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, int rpp, int G) {
+  constexpr bool CD = MODE != 0;
   extern __shared__ __align__(16) float sm[];
   const int seq = blockIdx.z, head = blockIdx.y;
   const int tok0 = a.seqs[seq * 8 + 0], n = a.seqs[seq * 8 + 1], pos0 = a.seqs[seq * 8 + 2], slot = a.seqs[seq * 8 + 3];
-  const int D = a.dim, Dv = a.vdim;
+  const int D = a.dim, Dv = a.vdim + a.ones_col;       // value columns of the state, the column of ones included
   const int tcols = kThreads / P, cols = tcols * NC;   // columns per thread group, per CTA
   const int part = threadIdx.x / tcols, jj = threadIdx.x % tcols;
   int j[NC];
@@ -69,6 +77,7 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
   const int ps = rpp + 4, Dp = P * ps;     // padded slice and row length
   float* vs = sm + static_cast<size_t>(G) * 3 * Dp;   // [G][cols]
   float* os = vs + G * cols;                          // [G][P][cols]
+  float* ds = os + G * P * cols;                      // [G] the round's decays (MODE 2)
   const T* base = static_cast<const T*>(a.qkv);
   float* Sg = a.states + ((static_cast<long long>(slot) * a.heads + head) * D) * Dv;
   float S[NC][kRows];
@@ -81,7 +90,7 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
     }
   const int slice_elems = P * rpp;
   const bool silu = a.act == GLA_ACT_SILU;
-  const float hdecay = CD ? a.head_decay[head] : 0.f;
+  const float hdecay = MODE == 1 ? a.head_decay[head] : 0.f;
   for (int g0 = 0; g0 < n; g0 += G) {
     const int gn = min(G, n - g0);
     __syncthreads();
@@ -97,6 +106,7 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
           const T* rp = base + row * a.ld;
           float qv = ldf(rp + a.q_off + c), kv = ldf(rp + a.k_off + c);
           if (silu) { qv = siluf_(qv); kv = siluf_(kv); }
+          if (MODE == 2) kv *= __ldg(a.tok_kscale + row * a.heads + head);
           s3[(tt * 3) * Dp] = qv * a.q_scale;
           s3[(tt * 3 + 1) * Dp] = kv;
           if (!CD) s3[(tt * 3 + 2) * Dp] = __ldg(a.z + row * (a.heads * D) + c);
@@ -107,12 +117,16 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
     }
     for (int e = threadIdx.x; e < gn * cols; e += kThreads) {
       const int tt = e / cols, c = e - tt * cols, jc = blockIdx.x * cols + c;
-      float vv = jc < Dv ? ldf(base + static_cast<long long>(tok0 + g0 + tt) * a.ld + a.v_off + head * Dv + jc) : 0.f;
+      float vv = jc < a.vdim ? ldf(base + static_cast<long long>(tok0 + g0 + tt) * a.ld + a.v_off + head * a.vdim + jc) : 0.f;
       if (silu) vv = siluf_(vv);
+      if (jc == a.vdim && a.ones_col) vv = 1.f;
       vs[e] = vv;
     }
+    if (MODE == 2)
+      for (int tt = threadIdx.x; tt < gn; tt += kThreads) ds[tt] = __ldg(a.tok_decay + static_cast<long long>(tok0 + g0 + tt) * a.heads + head);
     __syncthreads();
     for (int tt = 0; tt < gn; ++tt) {
+      const float decay = MODE == 2 ? ds[tt] : hdecay;
       float v[NC], o[NC][4];
 #pragma unroll
       for (int c = 0; c < NC; ++c) { v[c] = vs[tt * cols + jj + c * tcols]; o[c][0] = o[c][1] = o[c][2] = o[c][3] = 0.f; }
@@ -122,7 +136,7 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
 #pragma unroll
       for (int m = 0; m < kRows / 4; ++m) {
         if (4 * m < rpp) {
-          const float4 qa = q4[m], ka = k4[m], aa = CD ? make_float4(hdecay, hdecay, hdecay, hdecay) : a4[m];
+          const float4 qa = q4[m], ka = k4[m], aa = CD ? make_float4(decay, decay, decay, decay) : a4[m];
 #pragma unroll
           for (int c = 0; c < NC; ++c) {
             float* Sc = S[c] + 4 * m;
@@ -189,11 +203,15 @@ __global__ void recurrent_out_gate_kernel(OutGateArgs a, long long units) {
     if (p >= units) return;
     t = p / a.heads; c0 = static_cast<int>(p - t * a.heads) * a.vdim; n = a.vdim; first = lane; step = 32;
   }
-  const float* op = a.o + t * (static_cast<long long>(a.heads) * a.vdim) + c0;
+  const int ostride = a.o_stride > 0 ? a.o_stride : a.vdim;
+  const float* op = a.joint ? a.o + t * (static_cast<long long>(a.heads) * a.vdim) : a.o + (t * a.heads + c0 / a.vdim) * ostride;
+  // a normalised recurrence: the row's outputs are divided by max(|n . q|, floor) + den_eps before the norm
+  const float dinv = a.den_floor ? 1.0f / (fmaxf(fabsf(op[a.vdim]), a.den_floor[t * a.heads + c0 / a.vdim]) + a.den_eps) : 1.0f;
+  const float* w = a.w + (a.w_full ? c0 : 0);
   const T* g = static_cast<const T*>(a.g) + t * a.ldg + c0;
   T* y = static_cast<T*>(a.y) + t * a.ldy + c0;
   float ss = 0.f;
-  for (int i = first; i < n; i += step) ss = fmaf(op[i], op[i], ss);
+  for (int i = first; i < n; i += step) { const float v = op[i] * dinv; ss = fmaf(v, v, ss); }
   for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
   if (a.joint) {
     if (lane == 0) red[wrp] = ss;
@@ -206,16 +224,66 @@ __global__ void recurrent_out_gate_kernel(OutGateArgs a, long long units) {
     const float gv = ldf(g + i);
     const float sg = 1.0f / (1.0f + expf(-gv));
     const float gate = a.gate_act == GATE_SIGMOID ? sg : gv * sg;
-    stf(y + i, op[i] * inv * a.w[i] * gate * a.out_scale);
+    stf(y + i, op[i] * dinv * inv * w[i] * gate * a.out_scale);
   }
 }
 
+// The scalar gates of the matrix-memory recurrence (MlstmGateArgs).  One CTA per (head, sequence) walks the sequence's
+// tokens in rounds: all threads turn a round's pre-activations into the log gates (accurate tanhf, log1pf, expf), ONE
+// thread runs the chain m_t = max(f_t + m_(t-1), i_t) over the round from shared memory (an add and a max per token,
+// the same operations in the same order however the sequence was cut into steps), all threads turn (i, f, m) into the
+// three factors the scan and the output stage read.
+constexpr int kGateRound = 512;
+__global__ void __launch_bounds__(128) mlstm_gates_kernel(MlstmGateArgs a) {
+  __shared__ float li[kGateRound], lf[kGateRound], ms[kGateRound + 1];
+  const int head = blockIdx.x, seq = blockIdx.y;
+  const int tok0 = a.seqs[seq * 8 + 0], n = a.seqs[seq * 8 + 1], pos0 = a.seqs[seq * 8 + 2], slot = a.seqs[seq * 8 + 3];
+  float* mst = a.mstate + static_cast<long long>(slot) * a.heads + head;
+  if (threadIdx.x == 0) ms[0] = pos0 > 0 ? *mst : 0.f;
+  for (int g0 = 0; g0 < n; g0 += kGateRound) {
+    const int gn = min(kGateRound, n - g0);
+    for (int tt = threadIdx.x; tt < gn; tt += blockDim.x) {
+      const float* row = a.pre + static_cast<long long>(tok0 + g0 + tt) * a.ld;
+      float zi = row[head], zf = row[a.heads + head];
+      if (a.cap > 0.f) { zi = a.cap * tanhf(zi / a.cap); zf = a.cap * tanhf(zf / a.cap); }
+      li[tt] = zi;
+      lf[tt] = fminf(zf, 0.f) - log1pf(expf(-fabsf(zf)));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float m = ms[0];
+      for (int tt = 0; tt < gn; ++tt) { m = fmaxf(lf[tt] + m, li[tt]); ms[tt + 1] = m; }
+    }
+    __syncthreads();
+    for (int tt = threadIdx.x; tt < gn; tt += blockDim.x) {
+      const long long o = static_cast<long long>(tok0 + g0 + tt) * a.heads + head;
+      const float mp = ms[tt], mn = ms[tt + 1];
+      a.keep[o] = expf(lf[tt] + mp - mn);
+      a.take[o] = expf(li[tt] - mn);
+      a.floor[o] = expf(-mn);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) ms[0] = ms[gn];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && n > 0) *mst = ms[0];
+}
+
 }  // namespace
+
+int mlstm_gates(const MlstmGateArgs& a, cudaStream_t st) {
+  if (a.nseq <= 0) return 0;
+  if (!a.pre || !a.keep || !a.take || !a.floor || !a.mstate || !a.seqs || a.heads < 1 || a.ld < 2 * a.heads) return -1;
+  mlstm_gates_kernel<<<dim3(a.heads, a.nseq), 128, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 int recurrent_out_gate(const OutGateArgs& a, cudaStream_t st) {
   const long long units = a.joint ? a.T : static_cast<long long>(a.T) * a.heads;
   if (units <= 0) return 0;
   if (!a.o || !a.g || !a.w || !a.y || a.heads < 1 || a.vdim < 1) return -1;
+  if (a.joint && (a.o_stride > 0 || a.w_full || a.den_floor)) return -1;
+  if (a.den_floor && a.o_stride <= a.vdim) return -1;
   const int th = a.joint ? (a.heads * a.vdim >= 1024 ? 256 : 128) : 128;
   const unsigned grid = static_cast<unsigned>(a.joint ? units : (units + 3) / 4);
   if (a.t == DT_BF16) recurrent_out_gate_kernel<bf16><<<grid, th, 0, st>>>(a, units);
@@ -238,20 +306,24 @@ int gla_scan(const GlaArgs& a, cudaStream_t st) {
   int NC = (a.vdim >= 2 * tcols && ctas2 >= sms) ? 2 : 1;
   if (const char* e = getenv("B200_GLA_NC")) NC = atoi(e) == 2 && a.vdim >= 2 * tcols ? 2 : 1;   // A/B knob
   const int cols = tcols * NC;
-  dim3 grid((a.vdim + cols - 1) / cols, a.heads, a.nseq);
+  dim3 grid((a.vdim + a.ones_col + cols - 1) / cols, a.heads, a.nseq);
   int G = kGroup;
   if (const char* e = getenv("B200_GLA_GROUP")) G = std::max(1, atoi(e));   // A/B knob: tokens staged per round
-  auto smem_for = [&](int g) { return static_cast<size_t>(g) * (3 * P * (rows_per_part + 4) + (1 + P) * cols) * sizeof(float); };
+  auto smem_for = [&](int g) { return static_cast<size_t>(g) * (3 * P * (rows_per_part + 4) + (1 + P) * cols + 1) * sizeof(float); };
   while (G > 1 && smem_for(G) > 44 * 1024) G >>= 1;
   const size_t smem = smem_for(G);
   if (smem > 48 * 1024) return -1;
-  if (!a.head_decay) {
+  if (a.ones_col != 0 && a.ones_col != 1) return -1;
+  if (a.tok_decay) {
+    if (!a.tok_kscale || a.head_decay) return -1;
+  } else if (!a.head_decay) {
     if (!a.z || !a.z_bias) return -1;
     const long long total = static_cast<long long>(a.T) * a.heads * a.dim;
     if (total > 0) gla_decay_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(a.z, a.z_bias, a.heads * a.dim, a.inv_tau, total);
   }
-#define SCAN(T_, NC_) do { if (a.head_decay) gla_scan_kernel<T_, NC_, true><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); \
-                          else gla_scan_kernel<T_, NC_, false><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); } while (0)
+#define SCAN(T_, NC_) do { if (a.tok_decay) gla_scan_kernel<T_, NC_, 2><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); \
+                          else if (a.head_decay) gla_scan_kernel<T_, NC_, 1><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); \
+                          else gla_scan_kernel<T_, NC_, 0><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); } while (0)
   if (a.t == DT_BF16) {
     if (NC == 2) SCAN(bf16, 2); else SCAN(bf16, 1);
   } else {

@@ -7,8 +7,17 @@
 // owns one token row, updates the n streams in place, keeps u in shared memory, reduces mean(u^2) in a fixed order and
 // writes the normed row in the storage type of the projections.  With one stream and no mixing weights the same kernel
 // is the ordinary pre-norm residual step x <- x + y; h = rmsnorm(x).  Everything is fp32 up to the single rounding of h.
+//
+// Beside it, for designs with one residual and a norm on BOTH sides of every sublayer (mixers.h SandwichArgs): the
+// sublayer's output is RMS-normed before it is added, x <- x + norm_post(y + bias), and the next sublayer reads
+// norm_pre(x); one kernel per boundary, a CTA per token row, two fixed-order reductions.  And the sinusoidal position
+// embedding that fills such a residual.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <math.h>
+
+#include <vector>
 
 #include "mixers.h"
 
@@ -217,7 +226,140 @@ __global__ void __launch_bounds__(256) hyper_step_vec_kernel(HyperArgs a) {
 
 inline int threads_for(int W) { return W >= 2048 ? 256 : (W >= 256 ? 128 : 64); }
 
+// x[t] = embed[id] + sinusoid(pos).  The angle p * f is formed from the two-float frequency: a = fl(p * f_hi), the
+// rounding error of that product (one fma) plus p * f_lo is a correction e of a few ulps of a, and sin(a + e), cos(a + e)
+// follow from the accurate sinf / cosf of a by one step of the addition formulas.
+template <typename TW>
+__global__ void embed_sinusoid_kernel(const TW* embed, const int* ids, const int* pos, const float2* freq, float* x, int W, int vocab) {
+  const long long t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const float p = static_cast<float>(pos[t]);
+  const TW* e = embed + static_cast<long long>(id) * W;
+  float* xr = x + t * W;
+  for (int i = threadIdx.x; 2 * i < W; i += blockDim.x) {
+    const float2 f = freq[i];
+    const float a = p * f.x;
+    const float err = fmaf(p, f.x, -a) + p * f.y;
+    float sn, cs;
+    sincosf(a, &sn, &cs);
+    xr[2 * i] = ldf(e + 2 * i) + fmaf(err, cs, sn);
+    if (2 * i + 1 < W) xr[2 * i + 1] = ldf(e + 2 * i + 1) + fmaf(-err, sn, cs);
+  }
+}
+
+// sum over the CTA of v, the same in every thread: lanes by shuffles, warps in a fixed order
+__device__ __forceinline__ float cta_sum(float v, float* red) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
+  __syncthreads();   // red may still be read from the previous sum
+  if (lane == 0) red[wrp] = v;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+  return tot;
+}
+
+// VEC: four neighbouring columns per thread and round (W % 4 == 0, every row start 16-byte aligned)
+template <typename TY, typename TH, bool VEC>
+__global__ void __launch_bounds__(256) sandwich_step_kernel(SandwichArgs a) {
+  extern __shared__ __align__(16) float row[];   // [W]: the sublayer output with its bias, then the new residual row
+  __shared__ float red[8];
+  const int r = blockIdx.x;
+  const long long t = a.row_index ? a.row_index[r] : r;
+  float* x = a.x + t * a.W;
+  const TY* y = static_cast<const TY*>(a.y);
+  constexpr int C = VEC ? 4 : 1;
+  const int first = threadIdx.x * C, step = blockDim.x * C;
+  float inv_y = 1.f;
+  if (y) {
+    float ss = 0.f;
+    for (int i = first; i < a.W; i += step) {
+      float u[4];
+      if (VEC) { const float4 v = ld4(y + t * a.W + i); u[0] = v.x; u[1] = v.y; u[2] = v.z; u[3] = v.w; }
+      else u[0] = ldf(y + t * a.W + i);
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        if (a.y_bias) u[c] += a.y_bias[i + c];
+        ss = fmaf(u[c], u[c], ss);
+        row[i + c] = u[c];
+      }
+    }
+    if (a.post_w) inv_y = 1.0f / sqrtf(cta_sum(ss, red) / static_cast<float>(a.W) + a.eps);
+  }
+  float ss = 0.f;
+  for (int i = first; i < a.W; i += step) {
+    float xv[4];
+    if (VEC) { const float4 v = ld4(x + i); xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w; }
+    else xv[0] = x[i];
+    if (y) {
+#pragma unroll
+      for (int c = 0; c < C; ++c) xv[c] += a.post_w ? row[i + c] * inv_y * a.post_w[i + c] : row[i + c];   // each thread reads back what it wrote
+      if (VEC) st4(x + i, make_float4(xv[0], xv[1], xv[2], xv[3]));
+      else x[i] = xv[0];
+    }
+#pragma unroll
+    for (int c = 0; c < C; ++c) { ss = fmaf(xv[c], xv[c], ss); row[i + c] = xv[c]; }
+  }
+  if (!a.h) return;
+  TH* h = static_cast<TH*>(a.h) + static_cast<long long>(r) * a.W;
+  const float inv = a.pre_w ? 1.0f / sqrtf(cta_sum(ss, red) / static_cast<float>(a.W) + a.eps) : 1.f;
+  for (int i = first; i < a.W; i += step) {
+    if (VEC) {
+      const float4 u = ld4(row + i);
+      float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (a.pre_w) w = ld4(a.pre_w + i);
+      st4(h + i, a.pre_w ? make_float4(u.x * inv * w.x, u.y * inv * w.y, u.z * inv * w.z, u.w * inv * w.w) : u);
+    } else {
+      stf(h + i, a.pre_w ? row[i] * inv * a.pre_w[i] : row[i]);
+    }
+  }
+}
+
 }  // namespace
+
+int sinusoid_freq_table(float2* freq, int W, double base, cudaStream_t st) {
+  const int pairs = (W + 1) / 2;
+  if (pairs <= 0) return 0;
+  if (!(base > 0.0)) return -1;
+  std::vector<float2> h(pairs);
+  for (int i = 0; i < pairs; ++i) {
+    const double f = pow(base, -2.0 * i / W);
+    const float hi = static_cast<float>(f);
+    h[i] = make_float2(hi, static_cast<float>(f - static_cast<double>(hi)));
+  }
+  if (cudaMemcpyAsync(freq, h.data(), h.size() * sizeof(float2), cudaMemcpyHostToDevice, st) != cudaSuccess) return -2;
+  return cudaStreamSynchronize(st) == cudaSuccess ? 0 : -2;
+}
+
+int embed_sinusoid(const void* embed, DType tw, const int* ids, const int* pos, const float2* freq, float* x, int T, int W, int vocab,
+                   cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (W < 1 || !freq || !pos) return -1;
+  if (tw == DT_BF16) embed_sinusoid_kernel<bf16><<<T, threads_for(W), 0, st>>>(static_cast<const bf16*>(embed), ids, pos, freq, x, W, vocab);
+  else embed_sinusoid_kernel<float><<<T, threads_for(W), 0, st>>>(static_cast<const float*>(embed), ids, pos, freq, x, W, vocab);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int sandwich_step(const SandwichArgs& a, cudaStream_t st) {
+  if (a.rows <= 0) return 0;
+  if (!a.x || a.W < 1) return -1;
+  if (a.y && a.row_index) return -1;   // an update of chosen rows only would leave the residual inconsistent
+  if (!a.y && !a.h) return 0;
+  const size_t smem = static_cast<size_t>(a.W) * sizeof(float);
+  if (smem > 48 * 1024) return -1;
+  auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool vec = a.W % 4 == 0 && al16(a.x) && al16(a.y) && al16(a.h) && al16(a.y_bias) && al16(a.post_w) && al16(a.pre_w);
+  const int th = vec ? (a.W >= 1024 ? 256 : (a.W >= 512 ? 128 : 64)) : threads_for(a.W);
+#define SW(TY, TH) do { if (vec) sandwich_step_kernel<TY, TH, true><<<a.rows, th, smem, st>>>(a); else sandwich_step_kernel<TY, TH, false><<<a.rows, th, smem, st>>>(a); } while (0)
+  const bool y16 = a.y && a.ty == DT_BF16, h16 = a.h && a.th == DT_BF16;
+  if (y16 && h16) SW(bf16, bf16);
+  else if (y16) SW(bf16, float);
+  else if (h16) SW(float, bf16);
+  else SW(float, float);
+#undef SW
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 int embed_scaled(const void* embed, DType tw, const int* ids, float* x, int T, int W, int vocab, float scale, int streams,
                  long long stream_stride, cudaStream_t st) {

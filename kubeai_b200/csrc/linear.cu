@@ -1,4 +1,4 @@
-// Shape-agnostic linear layer: Y = act(X W^T) for any T, N, K, in bf16 or fp32 storage with fp32 accumulation.
+// Shape-agnostic linear layer: Y = act(X W^T + bias) for any T, N, K, in bf16 or fp32 storage with fp32 accumulation.
 // Three uses share one kernel family (mixers.h LinearArgs): a plain projection, one projection per head inside wider
 // rows (batch index = head), and expert-grouped rows (64-row tiles that each name their weight matrix).  It is the
 // projection path of every shape the tcgen05 GEMMs (gemm2_tcgen05.cu: bf16, K % 8 == 0, bf16 output) do not take:
@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(LinearArgs a) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = col0 + tx * 4 + j;
-      if (n < a.N) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act(a.row_scale ? acc[i][j] * rs : acc[i][j], a.act));
+      if (n < a.N) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act((a.row_scale ? acc[i][j] * rs : acc[i][j]) + (a.bias ? a.bias[n] : 0.f), a.act));
     }
   }
 }
@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(256) linear_tile_mma_kernel(LinearArgs a) {
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int n = col0 + 32 * wn + 8 * nb + 2 * t4 + j;
-        if (n < a.N) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act(a.row_scale ? acc[nb][2 * half + j] * rs : acc[nb][2 * half + j], a.act));
+        if (n < a.N) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act((a.row_scale ? acc[nb][2 * half + j] * rs : acc[nb][2 * half + j]) + (a.bias ? a.bias[n] : 0.f), a.act));
       }
   }
 }
@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(LinearArgs a) {
       float v = acc[t];
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == 0) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act(a.row_scale ? v * a.row_scale[t] : v, a.act));
+      if (lane == 0) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act((a.row_scale ? v * a.row_scale[t] : v) + (a.bias ? a.bias[n] : 0.f), a.act));
     }
   }
 }
@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(256) linear_picked_rows_kernel(LinearArgs a, P
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) st1(static_cast<TY*>(a.Y) + dst * a.ldy + n, apply_act(a.row_scale ? acc * a.row_scale[r] : acc, a.act));
+  if (lane == 0) st1(static_cast<TY*>(a.Y) + dst * a.ldy + n, apply_act((a.row_scale ? acc * a.row_scale[r] : acc) + (a.bias ? a.bias[n] : 0.f), a.act));
 }
 
 template <typename TX, typename TW, typename TY>

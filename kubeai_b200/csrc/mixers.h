@@ -4,7 +4,9 @@
 // head), latent attention (paged low-rank KV with a shared rotated key and a sliding window), softmax attention over
 // paged keys and values with grouped heads, a sliding window and kept first tokens, hyper-connections (several residual
 // streams read and written through small mixing weights) with RMS norm, expert routing (softmax or sigmoid scores,
-// optionally group-limited), and the gated activations they use.
+// optionally group-limited, or a softmax over the chosen logits), the matrix-memory recurrence with exponential gating
+// (mLSTM), a sinusoidal position embedding, a residual step with a norm on both sides of the sublayer, and the gated
+// activations they use.
 //
 // Storage type: every activation / weight matrix is either bf16 or fp32 (DType); the residual stream, recurrent
 // states, router scores, decays, softmax and norm statistics are always fp32.  All pointers are device pointers.
@@ -28,6 +30,7 @@ enum LinearAct { LIN_NONE = 0, LIN_RELU2 = 1 };   // epilogue on the fp32 accumu
 //     a negative entry skips the tile (expert-grouped rows padded to the tile size).
 //   row_scale (optional, fp32): the accumulator of row t is multiplied by row_scale[t] before act, which is the product
 //     of the scaled input row, (s x) W^T = s (x W^T), without a scaled copy of x.
+//   bias (optional, fp32 [N]): added to the (scaled) accumulator before act.
 // The accumulation order of one output element never depends on T or on the other rows (k ascending inside a tile
 // kernel, a fixed lane pattern in the few-row kernel), so a row's result does not depend on what shares the batch.
 struct LinearArgs {
@@ -40,9 +43,10 @@ struct LinearArgs {
   const int* tile_group;
   int act;
   const float* row_scale;
+  const float* bias;
 };
 inline LinearArgs linear_args(const void* X, DType tx, const void* W, DType tw, void* Y, DType ty, int T, int N, int K) {
-  LinearArgs a = {X, W, Y, tx, tw, ty, T, N, K, K, K, N, 1, 0, 0, 0, nullptr, nullptr, LIN_NONE, nullptr};
+  LinearArgs a = {X, W, Y, tx, tw, ty, T, N, K, K, K, N, 1, 0, 0, 0, nullptr, nullptr, LIN_NONE, nullptr, nullptr};
   return a;
 }
 int linear(const LinearArgs& a, cudaStream_t st);
@@ -67,8 +71,11 @@ int embed_bigram(const void* embed, const void* bigram, DType tw, const int* ids
 int residual_dyt(float* x, const void* a, const void* f, DType ta, float mult, const float* w, const float* b, const float* alpha,
                  void* y, DType ty, const int* row_index, int rows, int W, cudaStream_t st);
 // Clamped gated unit: row t of gu (leading dimension ldgu) holds gate [F] | up [F]; g = min(gate, limit), u = clamp(up, -limit, limit),
-// y = g * sigmoid(slope * g) * (u + 1)
-int glu_clamped(const void* gu, int ldgu, void* y, int ldy, DType t, int T, int F, float limit, float slope, cudaStream_t st);
+// y = g * sigmoid(slope * g) * (u + up_offset).  limit = INFINITY, slope = 1, up_offset = 0 is the plain SiLU-gated unit.
+int glu_clamped(const void* gu, int ldgu, void* y, int ldy, DType t, int T, int F, float limit, float slope, cudaStream_t st,
+                float up_offset = 1.0f);
+// y[t, i] = act(y[t, i] + bias[i]) in place, i < n (leading dimension ldy; bias fp32, may be null; act: LinearAct)
+int bias_act(void* y, int ldy, const float* bias, int act, DType t, int T, int n, cudaStream_t st);
 // y[t, i] *= sigmoid(g[t, i]), i < n (leading dimensions ldy, ldg)
 int sigmoid_gate(void* y, int ldy, const void* g, int ldg, DType t, int T, int n, cudaStream_t st);
 // p[i] = offset + scale * u_i, u uniform in [-1, 1) from a counter hash of (seed, i): seeded random weights for benchmarks
@@ -84,6 +91,11 @@ int argmax_f32(const float* logits, int* out, int S, int V, cudaStream_t st);
 // head_decay (optional, fp32 [heads]): every key channel of head h decays by the constant head_decay[h] (the scalar-decay
 // linear attention, S <- lambda_h S + k v^T); z and z_bias are then unused and may be null.  act: GLA_ACT_SILU applies
 // x * sigmoid(x) to q, k and v as they are read (q before q_scale).
+// tok_decay with tok_kscale (fp32 [T, heads]): every channel of head h decays by tok_decay[t, h] at token t and the key is
+// multiplied by tok_kscale[t, h] as it is read, S <- d_t S + (s_t k_t) v_t^T (scalar gates that change from token to
+// token); z, z_bias and head_decay are then unused.  ones_col = 1 appends one value column that is 1 for every token: the
+// state becomes [dim][vdim + 1], o becomes [T, heads * (vdim + 1)], and the extra column carries the running key sum
+// n_t = d_t n_(t-1) + s_t k_t and its product n_t . q_t, which normalised recurrences divide by.
 enum GlaAct { GLA_ACT_NONE = 0, GLA_ACT_SILU = 1 };
 struct GlaArgs {
   const void* qkv; DType t; int ld, q_off, k_off, v_off;
@@ -94,6 +106,8 @@ struct GlaArgs {
   float* o;
   const float* head_decay = nullptr;
   int act = GLA_ACT_NONE;
+  const float* tok_decay = nullptr; const float* tok_kscale = nullptr;
+  int ones_col = 0;
 };
 int gla_scan(const GlaArgs& a, cudaStream_t st);
 // y[t, h * vdim + :] (leading dimension ldy) = o[t, h, :] / sqrt(mean(o^2) + eps) * w * silu(g[t, h, :])   (w: fp32 [vdim], shared by the heads)
@@ -103,13 +117,32 @@ int gla_out_gate(const float* o, const void* g, int ldg, const float* w, float e
 // over the token's concatenated heads with w [heads * vdim] (joint = true); the gate is silu(g) or sigmoid(g); the result
 // is multiplied by out_scale before it is rounded to the storage type.
 enum GateAct { GATE_SILU = 0, GATE_SIGMOID = 1 };
+// Per-head form only: o_stride (0: vdim) is the distance between two heads' rows of o; w_full = true reads the weight as
+// [heads * vdim] (every head its own) instead of [vdim]; with den_floor (fp32 [T, heads]) a head's row holds vdim outputs
+// and, behind them, the normaliser product n . q, and the outputs are divided by max(|n . q|, den_floor[t, h]) + den_eps
+// before the norm.
 struct OutGateArgs {
   const float* o; const void* g; int ldg; const float* w; float eps;
   void* y; int ldy; DType t;
   int T, heads, vdim;
   bool joint; int gate_act; float out_scale;
+  int o_stride = 0; bool w_full = false;
+  const float* den_floor = nullptr; float den_eps = 0.f;
 };
 int recurrent_out_gate(const OutGateArgs& a, cudaStream_t st);
+// The scalar gates of the matrix-memory recurrence with exponential gating (mLSTM), per token and head, in fp32:
+//   log input gate  i = cap * tanh(zi / cap),   log forget gate  f = logsigmoid(cap * tanh(zf / cap))   (cap <= 0: no cap)
+//   running log-scale  m_t = max(f_t + m_(t-1), i_t),  m before the first token of a sequence is 0
+//   keep[t, h] = exp(f + m_(t-1) - m_t),  take[t, h] = exp(i - m_t),  floor[t, h] = exp(-m_t)
+// so that the stored state is the true one divided by exp(m): S_t = keep S_(t-1) + take k v^T (gla_scan with tok_decay =
+// keep, tok_kscale = take).  pre: fp32 [T, ld] pre-activations with bias, zi of head h at column h, zf at heads + h.
+// mstate: fp32 [slot][heads], read when the sequence's first position is above 0, written at the end of the step.
+struct MlstmGateArgs {
+  const float* pre; int ld; float cap;
+  float* keep; float* take; float* floor;
+  float* mstate; const int* seqs; int nseq; int heads;
+};
+int mlstm_gates(const MlstmGateArgs& a, cudaStream_t st);
 
 // ---------------------------------------------------------------- latent attention (latent_attention.cu)
 // Rotation table for interleaved pairs (2i, 2i+1): cs[p][i] = (cos, sin)(p * base^(-2i/dims)), computed in double.
@@ -150,6 +183,11 @@ int rope_table_yarn(float2* table, int max_pos, int dims, double base, const Rop
 // rotated by the token's position (pairs (2i, 2i+1)), then each head is divided by its root mean square over dim (eps
 // inside the root; unit_norm = false skips that).  Queries go to qn (fp32 [T, heads * dim]); keys and values
 // (kv_heads x vdim at v) go to the token's cache row: cache [slot][kv_heads * dim | kv_heads * vdim] of type t.
+// q_norm_w / k_norm_w (optional, fp32 [dim], shared by the heads) multiply the normed query / key.  q_gain_every > 0
+// multiplies the query at position p by 1 + q_gain_coef * ln(floor((p + 1) / q_gain_every) + 1).  v_blend (optional, type
+// t, [T, kv_heads * vdim] with leading dimension ld_blend): the cached value is (1 - v_lambda) v + v_lambda v_blend (the
+// same token's values of an earlier layer); v_raw_out (optional, same shape, leading dimension ld_raw) receives v as it
+// came in, for later layers to blend with.  rot_dims = 0 needs no table.
 struct QkPrepArgs {
   const void* q; const void* k; const void* v; int ld; DType t;   // column blocks of one row-major buffer
   const float2* rope; int rot_dims;
@@ -157,12 +195,18 @@ struct QkPrepArgs {
   const int* positions; const int* slots;
   float* qn; void* cache;
   int T, heads, kv_heads, dim, vdim;
+  const float* q_norm_w = nullptr; const float* k_norm_w = nullptr;
+  float q_gain_coef = 0.f; int q_gain_every = 0;
+  const void* v_blend = nullptr; int ld_blend = 0; float v_lambda = 0.f;
+  void* v_raw_out = nullptr; int ld_raw = 0;
 };
 int qk_rope_norm_cache(const QkPrepArgs& a, cudaStream_t st);
 // Softmax attention of token t (position p of its sequence) over the cached keys j <= p with p - j < window or
 // j < keep_first (kept tokens stay at their own positions).  Query head h reads key/value head h / (heads / kv_heads).
 // score = qn . k * scale, softmax in fp32.  y[t, h * vdim + :] = out_scale * o * sigmoid(gate[t, h * vdim + :]) (gate of
 // type t with leading dimension ldg, may be null: no gate), rounded once to type t (leading dimension ldy).
+// softcap > 0: score <- softcap * tanh(score / softcap) after the scale.  gate_per_head: the gate holds one number per
+// (token, head), gate[t * ldg + h], instead of one per output column.
 struct WindowAttnArgs {
   const float* qn; const void* cache; DType t;
   const int* positions; const int* seq_of_tok; const int* block_tables; int max_blocks, page;
@@ -170,6 +214,7 @@ struct WindowAttnArgs {
   void* y; int ldy;
   int T, heads, kv_heads, dim, vdim, window, keep_first; float scale;
   const int* seqs; int nseq; int max_ctx;
+  float softcap = 0.f; bool gate_per_head = false;
 };
 int window_attention(const WindowAttnArgs& a, cudaStream_t st);
 
@@ -192,12 +237,35 @@ struct HyperArgs {
 };
 int hyper_step(const HyperArgs& a, cudaStream_t st);
 
+// Sinusoidal positions added to the embedding: x[t] = embed[ids[t]] + s(pos[t]), where column c of s(p) belongs to the
+// pair i = c / 2 with angle p * base^(-2i/W) and carries its sine (c even) or cosine (c odd).  freq: [(W + 1) / 2] float2,
+// the double-precision frequency of every pair split into two floats (sinusoid_freq_table), so that the angle p * f keeps
+// its low bits at large positions; x is fp32 [T, W].
+int sinusoid_freq_table(float2* freq, int W, double base, cudaStream_t st);
+int embed_sinusoid(const void* embed, DType tw, const int* ids, const int* pos, const float2* freq, float* x, int T, int W, int vocab,
+                   cudaStream_t st);
+// One boundary between two sublayers of a design with a norm on both sides of every sublayer, on one fp32 residual.
+// For r < rows, t = row_index ? row_index[r] : r:
+//   if (y)  u = y[t] + y_bias;  x[t] <- x[t] + (post_w ? u / sqrt(mean(u^2) + eps) * post_w : u)      (y_bias fp32, may be null)
+//   if (h)  h[r] = pre_w ? x[t] / sqrt(mean(x[t]^2) + eps) * pre_w : x[t]                             (fp32 statistics; h of type th)
+// post_w and pre_w are the multiplicative weights themselves (a stored offset from one is added at load).
+struct SandwichArgs {
+  float* x;
+  const void* y; DType ty; const float* y_bias;
+  const float* post_w; const float* pre_w; float eps;
+  void* h; DType th;
+  const int* row_index; int rows; int W;
+};
+int sandwich_step(const SandwichArgs& a, cudaStream_t st);
+
 // ---------------------------------------------------------------- mixture of experts (moe.cu)
 // scores: fp32 [T, E] router logits in, clobbered.  softmax over E; experts form `groups` equal groups of neighbours, a
 // group's score is its largest member, only the `keep` best groups are eligible; the `top` largest eligible scores are
 // chosen (ties: lower index) and used unchanged as weights.  topk_ids / topk_w: [T, top].
-// score_fn: MOE_SOFTMAX as above, MOE_SIGMOID scores every expert by sigmoid(z) on its own (no normalisation over E).
-enum MoeScore { MOE_SOFTMAX = 0, MOE_SIGMOID = 1 };
+// score_fn: MOE_SOFTMAX as above, MOE_SIGMOID scores every expert by sigmoid(z) on its own (no normalisation over E),
+// MOE_TOP_SOFTMAX ranks the experts by the logits themselves and weights the chosen ones by the softmax over the chosen
+// logits only.
+enum MoeScore { MOE_SOFTMAX = 0, MOE_SIGMOID = 1, MOE_TOP_SOFTMAX = 2 };
 // ld: leading dimension of scores (0: E); columns past E are left alone (a design may keep other fp32 outputs there).
 int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st,
               int score_fn = MOE_SOFTMAX, int ld = 0);

@@ -109,5 +109,6 @@ Model* engine_model(b200_engine* e);
 
 std::unique_ptr<Model> make_nomanex(const JVal& config, DType dtype, std::string* err);
 std::unique_ptr<Model> make_zinavik(const JVal& config, DType dtype, std::string* err);
+std::unique_ptr<Model> make_mulenex(const JVal& config, DType dtype, std::string* err);
 
 }  // namespace b200

@@ -12,6 +12,7 @@ struct Entry {
 const Entry kModels[] = {
     {"Nomanex", make_nomanex},
     {"Zinavik", make_zinavik},
+    {"Mulenex", make_mulenex},
 };
 }  // namespace
 

@@ -3,7 +3,8 @@
 //
 // Routing of one token: s = softmax(z) over all E experts; the experts form `groups` equal groups of neighbours, a group
 // is ranked by its largest s, only the `keep` best groups stay eligible; the `top` largest eligible s win, ties to the
-// lower index, and s itself (not renormalised) is the weight.  A pair's result never depends on which other pairs
+// lower index, and s itself (not renormalised) is the weight.  Other forms score by sigmoid(z) alone, or rank by z and
+// weight the winners by the softmax over the winners' z only.  A pair's result never depends on which other pairs
 // share its tile, and the combine adds a token's choices in the order the router picked them.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -22,8 +23,12 @@ __global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, in
   if (t >= T) return;
   const int lane = threadIdx.x & 31;
   float* s = scores + static_cast<long long>(t) * ld;
+  // scores of the other forms lie in [0, 1]; raw logits may be anything, so their "nothing yet" mark is the lowest float
+  const float none = score_fn == MOE_TOP_SOFTMAX ? -FLT_MAX : -1.f;
   if (score_fn == MOE_SIGMOID) {
     for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
+  } else if (score_fn == MOE_TOP_SOFTMAX) {
+    for (int e = lane; e < E; e += 32) s[e] = fmaxf(s[e], -0.5f * FLT_MAX);   // a logit stays above the mark
   } else {
     float mx = -FLT_MAX;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
@@ -39,11 +44,11 @@ __global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, in
   // keep the best groups: bit g of `kept` (lane-uniform); groups <= 64
   unsigned long long kept = 0;
   for (int r = 0; r < keep; ++r) {
-    float best = -1.f;
+    float best = none;
     int bg = 0x7fffffff;
     for (int g = lane; g < groups; g += 32) {
       if (kept >> g & 1ull) continue;
-      float gm = -1.f;
+      float gm = none;
       for (int e = g * per; e < (g + 1) * per; ++e) gm = fmaxf(gm, s[e]);
       if (gm > best) { best = gm; bg = g; }
     }
@@ -54,8 +59,9 @@ __global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, in
     }
     if (bg != 0x7fffffff) kept |= 1ull << bg;
   }
+  float first = 0.f, sum = 0.f;   // MOE_TOP_SOFTMAX: the largest chosen logit and the sum of exp(logit - first) over the chosen
   for (int k = 0; k < top; ++k) {
-    float best = -1.f;
+    float best = none;
     int be = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
       if (!(kept >> (e / per) & 1ull)) continue;
@@ -68,12 +74,21 @@ __global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, in
       if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
     }
     if (be == 0x7fffffff) { be = 0; best = 0.f; }
+    if (k == 0) first = best;
+    sum += expf(best - first);
     if (lane == 0) {
       topk_ids[static_cast<long long>(t) * top + k] = be;
       topk_w[static_cast<long long>(t) * top + k] = best;
-      s[be] = -1.f;
+      s[be] = none;
     }
     __syncwarp();
+  }
+  if (score_fn == MOE_TOP_SOFTMAX) {
+    const float inv = 1.0f / sum;
+    for (int k = lane; k < top; k += 32) {
+      float* w = topk_w + static_cast<long long>(t) * top + k;
+      *w = expf(*w - first) * inv;
+    }
   }
 }
 

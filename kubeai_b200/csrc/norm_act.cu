@@ -1,5 +1,6 @@
 // Elementwise kernels of the fp32-residual model designs (mixers.h): hashed bigram embedding, Dynamic-Tanh norm fused
-// with the residual update that precedes it, the clamped gated unit, a sigmoid output gate and an fp32 argmax.
+// with the residual update that precedes it, the (optionally clamped) gated unit, bias + activation in place, a sigmoid
+// output gate and an fp32 argmax.
 // Every transcendental is evaluated in fp32 with the accurate library functions (tanhf, expf), not the fast intrinsics:
 // the same kernels serve the fp32 model mode.
 #include <cuda_bf16.h>
@@ -51,14 +52,25 @@ __global__ void residual_dyt_kernel(float* x, const TA* a, const TA* f, float mu
 }
 
 template <typename T>
-__global__ void glu_clamped_kernel(const T* gu, int ldgu, T* y, int ldy, int F, float limit, float slope, long long total) {
+__global__ void glu_clamped_kernel(const T* gu, int ldgu, T* y, int ldy, int F, float limit, float slope, float up_offset, long long total) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long long t = i / F;
   const int c = static_cast<int>(i - t * F);
   const float g = fminf(ldf(gu + t * ldgu + c), limit);
   const float u = fminf(fmaxf(ldf(gu + t * ldgu + F + c), -limit), limit);
-  stf(y + t * ldy + c, g * sigmoidf_(slope * g) * (u + 1.0f));
+  stf(y + t * ldy + c, g * sigmoidf_(slope * g) * (u + up_offset));
+}
+
+template <typename T>
+__global__ void bias_act_kernel(T* y, int ldy, const float* bias, int act, int n, long long total) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / n;
+  const int c = static_cast<int>(i - t * n);
+  float v = ldf(y + t * ldy + c) + (bias ? bias[c] : 0.f);
+  if (act == LIN_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
+  stf(y + t * ldy + c, v);
 }
 
 template <typename T>
@@ -145,12 +157,21 @@ int residual_dyt(float* x, const void* a, const void* f, DType ta, float mult, c
   return done();
 }
 
-int glu_clamped(const void* gu, int ldgu, void* y, int ldy, DType t, int T, int F, float limit, float slope, cudaStream_t st) {
+int glu_clamped(const void* gu, int ldgu, void* y, int ldy, DType t, int T, int F, float limit, float slope, cudaStream_t st, float up_offset) {
   const long long total = static_cast<long long>(T) * F;
   if (total <= 0) return 0;
   const unsigned grid = static_cast<unsigned>((total + 255) / 256);
-  if (t == DT_BF16) glu_clamped_kernel<bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(gu), ldgu, static_cast<bf16*>(y), ldy, F, limit, slope, total);
-  else glu_clamped_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(gu), ldgu, static_cast<float*>(y), ldy, F, limit, slope, total);
+  if (t == DT_BF16) glu_clamped_kernel<bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(gu), ldgu, static_cast<bf16*>(y), ldy, F, limit, slope, up_offset, total);
+  else glu_clamped_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(gu), ldgu, static_cast<float*>(y), ldy, F, limit, slope, up_offset, total);
+  return done();
+}
+
+int bias_act(void* y, int ldy, const float* bias, int act, DType t, int T, int n, cudaStream_t st) {
+  const long long total = static_cast<long long>(T) * n;
+  if (total <= 0) return 0;
+  const unsigned grid = static_cast<unsigned>((total + 255) / 256);
+  if (t == DT_BF16) bias_act_kernel<bf16><<<grid, 256, 0, st>>>(static_cast<bf16*>(y), ldy, bias, act, n, total);
+  else bias_act_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(y), ldy, bias, act, n, total);
   return done();
 }
 

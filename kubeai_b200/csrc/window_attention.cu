@@ -1,6 +1,8 @@
 // Softmax attention with grouped key/value heads over a paged cache, a sliding window and kept first tokens
 // (mixers.h WindowAttnArgs), with the preparation in front of it: interleaved rotary positions under YaRN-style
-// frequency scaling and a weightless unit-RMS norm of every query and key head (QkPrepArgs).
+// frequency scaling and a unit-RMS norm of every query and key head, optionally with a weight, a position-dependent query
+// gain and a blend of the values with an earlier layer's (QkPrepArgs).  Scores may be tanh-capped, the sigmoid output
+// gate is per output column or per head.
 //
 // Visibility of key j for the token at position p: j <= p and (p - j < window or j < keep_first).  The visible keys of
 // a token are therefore two runs, [0, min(keep_first, lo)) and [lo, p] with lo = max(0, p - window + 1); both kernels
@@ -47,7 +49,9 @@ __global__ void __launch_bounds__(128) qk_prep_kernel(QkPrepArgs a) {
   const int p = a.positions[t];
   const long long slot = a.slots[t];
   const int D = a.dim, half = a.rot_dims / 2, pairs = D / 2;
-  const float2* cs = a.rope + static_cast<long long>(p) * half;
+  const float2* cs = half ? a.rope + static_cast<long long>(p) * half : nullptr;
+  // the query gain of this position: 1 + coef ln(floor((p + 1) / every) + 1), in fp32 with the accurate logarithm
+  const float q_gain = a.q_gain_every > 0 ? 1.0f + a.q_gain_coef * logf(static_cast<float>((p + 1) / a.q_gain_every + 1)) : 1.0f;
   const long long crow = static_cast<long long>(a.kv_heads) * (D + a.vdim);
   T* cache = static_cast<T*>(a.cache) + slot * crow;
   for (int u = wrp; u < a.heads + a.kv_heads; u += nw) {
@@ -68,7 +72,8 @@ __global__ void __launch_bounds__(128) qk_prep_kernel(QkPrepArgs a) {
     }
     if ((D & 1) && lane == 0) { const float x = ldf(src + D - 1); ss = fmaf(x, x, ss); }
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float inv = a.unit_norm ? 1.0f / sqrtf(ss / static_cast<float>(D) + a.eps) : 1.0f;
+    const float inv = (a.unit_norm ? 1.0f / sqrtf(ss / static_cast<float>(D) + a.eps) : 1.0f) * (isq ? q_gain : 1.0f);
+    const float* nw = isq ? a.q_norm_w : a.k_norm_w;   // optional weight of the norm, shared by the heads
     for (int i = lane; i < pairs; i += 32) {
       float x0 = ldf(src + 2 * i), x1 = ldf(src + 2 * i + 1);
       if (i < half) {
@@ -76,23 +81,32 @@ __global__ void __launch_bounds__(128) qk_prep_kernel(QkPrepArgs a) {
         const float r0 = x0 * c.x - x1 * c.y, r1 = x1 * c.x + x0 * c.y;
         x0 = r0; x1 = r1;
       }
+      x0 *= inv; x1 *= inv;
+      if (nw) { x0 *= nw[2 * i]; x1 *= nw[2 * i + 1]; }
       if (isq) {
         float* dst = a.qn + (t * a.heads + u) * D;
-        dst[2 * i] = x0 * inv; dst[2 * i + 1] = x1 * inv;
+        dst[2 * i] = x0; dst[2 * i + 1] = x1;
       } else {
         T* dst = cache + static_cast<long long>(u - a.heads) * D;
-        stf(dst + 2 * i, x0 * inv); stf(dst + 2 * i + 1, x1 * inv);
+        stf(dst + 2 * i, x0); stf(dst + 2 * i + 1, x1);
       }
     }
     if ((D & 1) && lane == 0) {
-      const float x = ldf(src + D - 1) * inv;
+      const float x = ldf(src + D - 1) * inv * (nw ? nw[D - 1] : 1.0f);
       if (isq) a.qn[(t * a.heads + u) * D + D - 1] = x;
       else stf(cache + static_cast<long long>(u - a.heads) * D + D - 1, x);
     }
   }
   const T* v = static_cast<const T*>(a.v) + t * a.ld;
   T* vdst = cache + static_cast<long long>(a.kv_heads) * D;
-  for (int i = threadIdx.x; i < a.kv_heads * a.vdim; i += blockDim.x) vdst[i] = v[i];
+  const T* vb = a.v_blend ? static_cast<const T*>(a.v_blend) + t * a.ld_blend : nullptr;
+  T* vraw = a.v_raw_out ? static_cast<T*>(a.v_raw_out) + t * a.ld_raw : nullptr;
+  for (int i = threadIdx.x; i < a.kv_heads * a.vdim; i += blockDim.x) {
+    const T vi = v[i];
+    if (vraw) vraw[i] = vi;
+    if (vb) stf(vdst + i, (1.0f - a.v_lambda) * ldf(&vi) + a.v_lambda * ldf(vb + i));
+    else vdst[i] = vi;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------- attention, any head size
@@ -156,6 +170,7 @@ __global__ void __launch_bounds__(kWarpsDecode * 32) window_attn_kernel(WindowAt
       const int j = i < nk ? i : lo + (i - nk);
       row = static_cast<long long>(bt[j / a.page]) * a.page + j % a.page;
       s = dot_row(qs, cache + row * crow + koff, D, vec);
+      if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
     }
     float cm = s;
     for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, o));
@@ -211,7 +226,7 @@ __global__ void __launch_bounds__(kWarpsDecode * 32) window_attn_kernel(WindowAt
     for (int w = 0; w < kWarpsDecode; ++w)
       if (w < nwarps) o = fmaf(part[w * (Dv + 2) + 2 + c], f[w], o);
     o *= inv;
-    if (gate) o *= sigmoidf_(ldf(gate + t * a.ldg + static_cast<long long>(h) * Dv + c));
+    if (gate) o *= sigmoidf_(ldf(gate + t * a.ldg + (a.gate_per_head ? h : static_cast<long long>(h) * Dv + c)));
     stf(y + c, o * a.out_scale);
   }
 }
@@ -385,13 +400,22 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
     // mask, scale, running maximum.  A tile that every row of the warp sees whole (all keys at or before the warp's
     // first position and inside its last row's window) needs no per-element test.
     float mx[2] = {kMasked, kMasked};
+    if (a.softcap > 0.f) {
+      // score <- cap * tanh(scale * score / cap), tanh(z) = 1 - 2 / (exp(2 z) + 1); the scale that follows is then 1
+      const float pre = 2.0f * a.scale / a.softcap;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[nt][e] = a.softcap * (1.0f - __fdividef(2.0f, __expf(sc[nt][e] * pre) + 1.0f));
+    }
+    const float sscale = a.softcap > 0.f ? 1.0f : a.scale;
     const bool whole = cnt == kTileKeys && warp_ok && j0 + kTileKeys - 1 <= warp_pmin && (warp_pmax - j0 < a.window || j0 + kTileKeys <= a.keep_first);
     if (whole) {
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float v = sc[nt][e] * a.scale;
+          const float v = sc[nt][e] * sscale;
           sc[nt][e] = v;
           mx[e >> 1] = fmaxf(mx[e >> 1], v);
         }
@@ -402,7 +426,7 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
         for (int e = 0; e < 4; ++e) {
           const int hf = e >> 1, col = nt * 8 + 2 * t4 + (e & 1), j = j0 + col, p = prow[hf];
           const bool vis = rowok[hf] && col < cnt && j <= p && (p - j < a.window || j < a.keep_first);
-          const float v = vis ? sc[nt][e] * a.scale : kMasked;
+          const float v = vis ? sc[nt][e] * sscale : kMasked;
           sc[nt][e] = v;
           mx[hf] = fmaxf(mx[hf], v);
         }
@@ -470,7 +494,10 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
       if (i2 < nv) {
         const int c = 8 * i2 + 2 * t4;
         float v0 = o[i2][2 * hf] * inv, v1 = o[i2][2 * hf + 1] * inv;
-        if (gate) {
+        if (gate && a.gate_per_head) {
+          const float sg = sigmoidf_(__bfloat162float(gate[t * a.ldg + head]));
+          v0 *= sg; v1 *= sg;
+        } else if (gate) {
           const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(gate + t * a.ldg + static_cast<long long>(head) * Dv + c);
           v0 *= sigmoidf_(__bfloat162float(gv.x));
           v1 *= sigmoidf_(__bfloat162float(gv.y));
@@ -528,7 +555,7 @@ int window_attention(const WindowAttnArgs& a, cudaStream_t st) {
   const char* fe = getenv("B200_WATTN_MMA");
   const int force = fe ? atoi(fe) : -1;
   const bool fits = a.t == DT_BF16 && a.dim % 16 == 0 && a.vdim % 16 == 0 && a.dim <= 128 && a.vdim <= 128 && a.seqs && a.nseq > 0 && a.ldy % 2 == 0 &&
-                    (!a.gate || a.ldg % 2 == 0) && reinterpret_cast<uintptr_t>(a.cache) % 16 == 0;
+                    (!a.gate || a.gate_per_head || a.ldg % 2 == 0) && reinterpret_cast<uintptr_t>(a.cache) % 16 == 0;
   const bool want = force >= 0 ? force != 0 : (a.T >= 32 && a.T >= 8 * a.nseq);
   if (fits && want) {
     const int group = a.heads / a.kv_heads;
