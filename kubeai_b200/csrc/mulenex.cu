@@ -198,7 +198,7 @@ class Mulenex : public Model {
         s.v_mix = vm && vm->type == JVal::Bool && vm->b;
         if (s.v_mix) {
           if (first_blend < 0) { first_blend = static_cast<int>(i); s.v_first = true; }
-          else if (spec[first_blend].kv_heads * spec[first_blend].vdim != s.kv_heads * s.vdim) {
+          else if (spec[first_blend].kv_heads != s.kv_heads || spec[first_blend].vdim != s.vdim) {
             *err = "config: " + where + "blends values of another shape than layer " + std::to_string(first_blend) + "'s";
             return false;
           }

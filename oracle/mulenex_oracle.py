@@ -163,7 +163,7 @@ def moe_ff(P, mlp, h):
     chosen, weights = route(logits, mlp["router"]["top"])
     y = sum(w * gated_expert(P, "e%d." % e, h) for e, w in zip(chosen, weights))
     if mlp.get("shared"):
-        y = y + sigmoid(float(P["shared.sg"] @ h)) * gated_expert(P, "shared.", h)
+        y = y + sigmoid((P["shared.sg"] @ h).item()) * gated_expert(P, "shared.", h)
     return y
 
 
@@ -201,39 +201,65 @@ class MulenexOracle:
                 raise ValueError(ly["type"])
         return mixers
 
+    def new_state(self):
+        return dict(mixers=self.new_mixers(), pos=0)
+
+    def step(self, state, tok, layers=None, margin=None):
+        """One token through every layer; returns its logits.  `layers` collects the residual after every layer,
+        `margin` (a one-element list) the smallest routing margin met."""
+        W, cfg, eps = self.W, self.cfg, self.eps
+        x = W["embed"][tok] + position_row(state["pos"], cfg["width"])
+        state["pos"] += 1
+        for i, ly in enumerate(cfg["layers"]):
+            p = "l%d." % i
+            y = state["mixers"][i].step(norm_one_plus(x, W[p + "norm1"], eps))
+            x = x + norm_one_plus(y, W[p + "norm1b"], eps)
+            mlp = ly.get("mlp")
+            if mlp:
+                h = norm_one_plus(x, W[p + "norm2"], eps)
+                P = self.mlp_weights[i]
+                if mlp["kind"] == "dense":
+                    y = dense_ff(P, h)
+                else:
+                    y = moe_ff(P, mlp, h)
+                    if margin is not None:
+                        margin[0] = min(margin[0], routing_margin(P, mlp, h))
+                x = x + norm_one_plus(y, W[p + "norm2b"], eps)
+            if layers is not None:
+                layers.append(x.copy())
+        return W["head"] @ norm_one_plus(x, W["final.norm"], eps)
+
     def forward(self, tokens, return_layers=False, return_margins=False):
         """Logits [n, vocab] of every position (optionally the residual after every layer [layers, n, width], or per
         position the smallest routing margin over the layers)."""
-        W, cfg, eps = self.W, self.cfg, self.eps
-        mixers = self.new_mixers()
+        state = self.new_state()
         logits, layers, margins = [], [], []
-        for pos, tok in enumerate(tokens):
-            x = W["embed"][tok] + position_row(pos, cfg["width"])
-            per_layer, margin = [], math.inf
-            for i, ly in enumerate(cfg["layers"]):
-                p = "l%d." % i
-                y = mixers[i].step(norm_one_plus(x, W[p + "norm1"], eps))
-                x = x + norm_one_plus(y, W[p + "norm1b"], eps)
-                mlp = ly.get("mlp")
-                if mlp:
-                    h = norm_one_plus(x, W[p + "norm2"], eps)
-                    P = self.mlp_weights[i]
-                    if mlp["kind"] == "dense":
-                        y = dense_ff(P, h)
-                    else:
-                        y = moe_ff(P, mlp, h)
-                        margin = min(margin, routing_margin(P, mlp, h))
-                    x = x + norm_one_plus(y, W[p + "norm2b"], eps)
-                per_layer.append(x.copy())
+        for tok in tokens:
+            per_layer, margin = [], [math.inf]
+            logits.append(self.step(state, int(tok), per_layer, margin))
             layers.append(per_layer)
-            margins.append(margin)
-            logits.append(W["head"] @ norm_one_plus(x, W["final.norm"], eps))
+            margins.append(margin[0])
         out = np.stack(logits)
         if return_layers:
             return out, np.stack(layers).transpose(1, 0, 2)
         if return_margins:
             return out, np.array(margins)
         return out
+
+    def generate(self, prompt, n):
+        """Greedy continuation: (tokens, smallest top-1 / top-2 margin met on the way)."""
+        state = self.new_state()
+        lg = None
+        for t in prompt:
+            lg = self.step(state, int(t))
+        out, margin = [], float("inf")
+        for _ in range(n):
+            top = np.sort(lg)[-2:]
+            margin = min(margin, top[1] - top[0])
+            nxt = int(np.argmax(lg))
+            out.append(nxt)
+            lg = self.step(state, nxt)
+        return out, margin
 
     def routing_margins(self, tokens):
         return self.forward(tokens, return_margins=True)[1]

@@ -9,6 +9,7 @@ import sys
 import numpy as np
 import pytest
 
+import mulenex_util as mx
 from zinavik_util import layer, left, make_config, moe, oracle_for, random_weights, rel_err, right, write_model_dir
 
 pytestmark = pytest.mark.gpu
@@ -40,14 +41,27 @@ def schedule(seqs):
     return steps, rows
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_replayed_schedule_gives_the_oracles_logits(tmp_path, dtype):
+def zinavik_model():
     layers = [layer(l=left(heads=6, kv_heads=3, dim=16, vdim=16, window=21, keep_first=5), r=right(heads=2, dim=12, vdim=20), mlp=moe(experts=4, top=4, ff=24, shared=8)),
               layer(l=left(heads=2, kv_heads=2, dim=8, vdim=4, window=50, keep_first=0, rot_dims=4, scaling=None), mlp=None)]
     cfg = make_config(layers, width=40, vocab=70, streams=3, loop=(0, 1, 2))
     W = random_weights(cfg, seed=91)
+    return cfg, W, oracle_for(cfg, W)
+
+
+def mulenex_model():
+    layers = [mx.layer(mx.attention(heads=6, kv_heads=3, dim=16, vdim=16, q_temp=(0.8, 7)), mlp=mx.moe(experts=4, top=4, ff=24, shared=8)),
+              mx.layer(mx.mlstm(heads=2, dim=12, vdim=20), mlp=mx.dense(ff=48)), mx.layer(mx.attention(heads=3, kv_heads=3, dim=8, vdim=16, softcap=None), mlp=None)]
+    cfg = mx.make_config(layers, width=40, vocab=70)
+    W = mx.random_weights(cfg, seed=93)
+    return cfg, W, mx.oracle_for(cfg, W)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("model", [zinavik_model, mulenex_model])
+def test_replayed_schedule_gives_the_oracles_logits(tmp_path, dtype, model):
+    cfg, W, o = model()
     d = write_model_dir(tmp_path / "m", cfg, W)
-    o = oracle_for(cfg, W)
     rng = np.random.default_rng(92)
     seqs = {k: rng.integers(0, 70, size=n).tolist() for k, n in (("a", 90), ("b", 31), ("c", 71), ("d", 7), ("e", 45))}
     steps, rows = schedule(seqs)
