@@ -12,8 +12,9 @@
 // written once per step.
 //
 // The same scan serves recurrences whose gates are scalars per (token, head) (tok_decay / tok_kscale), among them the
-// matrix memory with exponential gating (mLSTM): its gates come from `mlstm_gates`, its normaliser n_t = d n + s k rides
-// along as one more value column of ones, and `recurrent_out_gate` divides by max(|n . q|, exp(-m)) before the norm.
+// matrix memory with exponential gating (mLSTM): its gates come from `mlstm_gates`, its normaliser n_t = d n + s k and the
+// product n . q ride along in the scan's first column block (GlaArgs::nstate / nq), and `recurrent_out_gate` divides by
+// max(|n . q|, exp(-m)) before the norm.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -59,14 +60,21 @@ __global__ void gla_decay_kernel(float* z, const float* bias, int HD, float inv_
 // MODE 0: learned per-channel decays, staged as a third row.  MODE 1: one constant decay per head (GlaArgs::head_decay): no
 // decay row is staged or read, the constant sits in a register.  MODE 2: one decay and one key scale per (token, head)
 // (GlaArgs::tok_decay / tok_kscale): the decays of a round's tokens sit in shared memory as G scalars, the key is scaled
-// as it is staged.  With GlaArgs::ones_col the state has one more value column whose v is 1 for every token.
-template <typename T, int NC, int MODE>
+// as it is staged.
+// NRM (with MODE 2): the CTAs of the first column block also carry the normaliser n [dim] of the head, n <- decay n + k
+// (what the scan does to a state column whose value is 1).  The threads of a row slice share its rows (thread jj owns rows
+// jj, jj + tcols, ... of the slice, at most kNormRows of them); every thread leaves its part of n . q in shared memory, and
+// the pass that writes the round's outputs sums the parts in a fixed order.
+// NE = rows of n per thread: 1 covers dim <= 128 (a slice has no more rows than threads), kNormRows the rest; 0 = no normaliser.
+constexpr int kNormRows = 8;
+template <typename T, int NC, int MODE, int NE>
 __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, int rpp, int G) {
   constexpr bool CD = MODE != 0;
+  constexpr bool NRM = NE > 0;
   extern __shared__ __align__(16) float sm[];
   const int seq = blockIdx.z, head = blockIdx.y;
   const int tok0 = a.seqs[seq * 8 + 0], n = a.seqs[seq * 8 + 1], pos0 = a.seqs[seq * 8 + 2], slot = a.seqs[seq * 8 + 3];
-  const int D = a.dim, Dv = a.vdim + a.ones_col;       // value columns of the state, the column of ones included
+  const int D = a.dim, Dv = a.vdim;
   const int tcols = kThreads / P, cols = tcols * NC;   // columns per thread group, per CTA
   const int part = threadIdx.x / tcols, jj = threadIdx.x % tcols;
   int j[NC];
@@ -78,6 +86,17 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
   float* vs = sm + static_cast<size_t>(G) * 3 * Dp;   // [G][cols]
   float* os = vs + G * cols;                          // [G][P][cols]
   float* ds = os + G * P * cols;                      // [G] the round's decays (MODE 2)
+  // behind the decays: [G][threads] partial n . q (NRM)
+  const bool nrm = NRM && blockIdx.x == 0;
+  float nv[NRM ? NE : 1];
+  if (NRM) {
+    const float* nst = a.nstate + (static_cast<long long>(slot) * a.heads + head) * D;
+#pragma unroll
+    for (int e = 0; e < NE; ++e) {
+      const int r = jj + e * tcols, i = i0 + r;
+      nv[e] = (nrm && r < rpp && i < D && pos0 > 0) ? nst[i] : 0.f;
+    }
+  }
   const T* base = static_cast<const T*>(a.qkv);
   float* Sg = a.states + ((static_cast<long long>(slot) * a.heads + head) * D) * Dv;
   float S[NC][kRows];
@@ -117,9 +136,8 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
     }
     for (int e = threadIdx.x; e < gn * cols; e += kThreads) {
       const int tt = e / cols, c = e - tt * cols, jc = blockIdx.x * cols + c;
-      float vv = jc < a.vdim ? ldf(base + static_cast<long long>(tok0 + g0 + tt) * a.ld + a.v_off + head * a.vdim + jc) : 0.f;
+      float vv = jc < Dv ? ldf(base + static_cast<long long>(tok0 + g0 + tt) * a.ld + a.v_off + head * Dv + jc) : 0.f;
       if (silu) vv = siluf_(vv);
-      if (jc == a.vdim && a.ones_col) vv = 1.f;
       vs[e] = vv;
     }
     if (MODE == 2)
@@ -149,6 +167,20 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
       }
 #pragma unroll
       for (int c = 0; c < NC; ++c) os[(tt * P + part) * cols + jj + c * tcols] = (o[c][0] + o[c][1]) + (o[c][2] + o[c][3]);
+      if (NRM && nrm) {
+        const float* qs = reinterpret_cast<const float*>(q4);
+        const float* ks = reinterpret_cast<const float*>(k4);
+        float nacc = 0.f;
+#pragma unroll
+        for (int e = 0; e < NE; ++e) {
+          const int r = jj + e * tcols;
+          if (r < rpp) {
+            nv[e] = fmaf(decay, nv[e], ks[r]);
+            nacc = fmaf(nv[e], qs[r], nacc);
+          }
+        }
+        (os + G * P * cols + G)[tt * kThreads + threadIdx.x] = nacc;   // summed over the threads by the output pass: no reduction inside the token chain
+      }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < gn * cols; e += kThreads) {
@@ -156,6 +188,22 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
       float o = 0.f;
       for (int pp = 0; pp < P; ++pp) o += os[(tt * P + pp) * cols + c];   // slices in a fixed order
       if (jc < Dv) a.o[static_cast<long long>(tok0 + g0 + tt) * (a.heads * Dv) + head * Dv + jc] = o;
+    }
+    if (NRM && nrm)
+      for (int tt = threadIdx.x >> 5; tt < gn; tt += kThreads / 32) {   // a warp per token: the threads' partial products in a fixed order
+        const int lane = threadIdx.x & 31;
+        const float* pq = ds + G + tt * kThreads;
+        float q = (pq[lane] + pq[lane + 32]) + (pq[lane + 64] + pq[lane + 96]);
+        for (int sft = 16; sft > 0; sft >>= 1) q += __shfl_xor_sync(0xffffffffu, q, sft);
+        if (lane == 0) a.nq[static_cast<long long>(tok0 + g0 + tt) * a.heads + head] = q;
+      }
+  }
+  if (NRM && nrm) {
+    float* nst = a.nstate + (static_cast<long long>(slot) * a.heads + head) * D;
+#pragma unroll
+    for (int e = 0; e < NE; ++e) {
+      const int r = jj + e * tcols, i = i0 + r;
+      if (r < rpp && i < D) nst[i] = nv[e];
     }
   }
 #pragma unroll
@@ -203,10 +251,10 @@ __global__ void recurrent_out_gate_kernel(OutGateArgs a, long long units) {
     if (p >= units) return;
     t = p / a.heads; c0 = static_cast<int>(p - t * a.heads) * a.vdim; n = a.vdim; first = lane; step = 32;
   }
-  const int ostride = a.o_stride > 0 ? a.o_stride : a.vdim;
-  const float* op = a.joint ? a.o + t * (static_cast<long long>(a.heads) * a.vdim) : a.o + (t * a.heads + c0 / a.vdim) * ostride;
-  // a normalised recurrence: the row's outputs are divided by max(|n . q|, floor) + den_eps before the norm
-  const float dinv = a.den_floor ? 1.0f / (fmaxf(fabsf(op[a.vdim]), a.den_floor[t * a.heads + c0 / a.vdim]) + a.den_eps) : 1.0f;
+  const float* op = a.o + t * (static_cast<long long>(a.heads) * a.vdim) + c0;
+  // a normalised recurrence: the head's outputs are divided by max(|n . q|, floor) + den_eps before the norm
+  const long long th = t * a.heads + c0 / a.vdim;
+  const float dinv = a.den_nq ? 1.0f / (fmaxf(fabsf(a.den_nq[th]), a.den_floor[th]) + a.den_eps) : 1.0f;
   const float* w = a.w + (a.w_full ? c0 : 0);
   const T* g = static_cast<const T*>(a.g) + t * a.ldg + c0;
   T* y = static_cast<T*>(a.y) + t * a.ldy + c0;
@@ -282,8 +330,8 @@ int recurrent_out_gate(const OutGateArgs& a, cudaStream_t st) {
   const long long units = a.joint ? a.T : static_cast<long long>(a.T) * a.heads;
   if (units <= 0) return 0;
   if (!a.o || !a.g || !a.w || !a.y || a.heads < 1 || a.vdim < 1) return -1;
-  if (a.joint && (a.o_stride > 0 || a.w_full || a.den_floor)) return -1;
-  if (a.den_floor && a.o_stride <= a.vdim) return -1;
+  if (a.joint && (a.w_full || a.den_nq)) return -1;
+  if (a.den_nq && !a.den_floor) return -1;
   const int th = a.joint ? (a.heads * a.vdim >= 1024 ? 256 : 128) : 128;
   const unsigned grid = static_cast<unsigned>(a.joint ? units : (units + 3) / 4);
   if (a.t == DT_BF16) recurrent_out_gate_kernel<bf16><<<grid, th, 0, st>>>(a, units);
@@ -306,14 +354,15 @@ int gla_scan(const GlaArgs& a, cudaStream_t st) {
   int NC = (a.vdim >= 2 * tcols && ctas2 >= sms) ? 2 : 1;
   if (const char* e = getenv("B200_GLA_NC")) NC = atoi(e) == 2 && a.vdim >= 2 * tcols ? 2 : 1;   // A/B knob
   const int cols = tcols * NC;
-  dim3 grid((a.vdim + a.ones_col + cols - 1) / cols, a.heads, a.nseq);
+  dim3 grid((a.vdim + cols - 1) / cols, a.heads, a.nseq);
   int G = kGroup;
   if (const char* e = getenv("B200_GLA_GROUP")) G = std::max(1, atoi(e));   // A/B knob: tokens staged per round
-  auto smem_for = [&](int g) { return static_cast<size_t>(g) * (3 * P * (rows_per_part + 4) + (1 + P) * cols + 1) * sizeof(float); };
+  auto smem_for = [&](int g) { return static_cast<size_t>(g) * (3 * P * (rows_per_part + 4) + (1 + P) * cols + 1 + (a.nstate ? kThreads : 0)) * sizeof(float); };
   while (G > 1 && smem_for(G) > 44 * 1024) G >>= 1;
   const size_t smem = smem_for(G);
   if (smem > 48 * 1024) return -1;
-  if (a.ones_col != 0 && a.ones_col != 1) return -1;
+  if ((a.nstate != nullptr) != (a.nq != nullptr) || (a.nstate && !a.tok_decay)) return -1;
+  if (a.nstate && rows_per_part > kNormRows * tcols) return -1;
   if (a.tok_decay) {
     if (!a.tok_kscale || a.head_decay) return -1;
   } else if (!a.head_decay) {
@@ -321,9 +370,12 @@ int gla_scan(const GlaArgs& a, cudaStream_t st) {
     const long long total = static_cast<long long>(a.T) * a.heads * a.dim;
     if (total > 0) gla_decay_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(a.z, a.z_bias, a.heads * a.dim, a.inv_tau, total);
   }
-#define SCAN(T_, NC_) do { if (a.tok_decay) gla_scan_kernel<T_, NC_, 2><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); \
-                          else if (a.head_decay) gla_scan_kernel<T_, NC_, 1><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); \
-                          else gla_scan_kernel<T_, NC_, 0><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); } while (0)
+  const bool one_row = rows_per_part <= tcols;
+#define SCAN(T_, NC_) do { if (a.tok_decay && a.nstate && one_row) gla_scan_kernel<T_, NC_, 2, 1><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); \
+                          else if (a.tok_decay && a.nstate) gla_scan_kernel<T_, NC_, 2, kNormRows><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); \
+                          else if (a.tok_decay) gla_scan_kernel<T_, NC_, 2, 0><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); \
+                          else if (a.head_decay) gla_scan_kernel<T_, NC_, 1, 0><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); \
+                          else gla_scan_kernel<T_, NC_, 0, 0><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); } while (0)
   if (a.t == DT_BF16) {
     if (NC == 2) SCAN(bf16, 2); else SCAN(bf16, 1);
   } else {

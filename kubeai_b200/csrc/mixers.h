@@ -93,9 +93,9 @@ int argmax_f32(const float* logits, int* out, int S, int V, cudaStream_t st);
 // x * sigmoid(x) to q, k and v as they are read (q before q_scale).
 // tok_decay with tok_kscale (fp32 [T, heads]): every channel of head h decays by tok_decay[t, h] at token t and the key is
 // multiplied by tok_kscale[t, h] as it is read, S <- d_t S + (s_t k_t) v_t^T (scalar gates that change from token to
-// token); z, z_bias and head_decay are then unused.  ones_col = 1 appends one value column that is 1 for every token: the
-// state becomes [dim][vdim + 1], o becomes [T, heads * (vdim + 1)], and the extra column carries the running key sum
-// n_t = d_t n_(t-1) + s_t k_t and its product n_t . q_t, which normalised recurrences divide by.
+// token); z, z_bias and head_decay are then unused.  With them, nstate (fp32 [slot][heads][dim]) and nq (fp32 [T, heads])
+// make the scan carry the running key sum n_t = d_t n_(t-1) + s_t k_t beside the state and write nq[t, h] = n_t . (q_t *
+// q_scale), which normalised recurrences divide by.
 enum GlaAct { GLA_ACT_NONE = 0, GLA_ACT_SILU = 1 };
 struct GlaArgs {
   const void* qkv; DType t; int ld, q_off, k_off, v_off;
@@ -107,7 +107,7 @@ struct GlaArgs {
   const float* head_decay = nullptr;
   int act = GLA_ACT_NONE;
   const float* tok_decay = nullptr; const float* tok_kscale = nullptr;
-  int ones_col = 0;
+  float* nstate = nullptr; float* nq = nullptr;
 };
 int gla_scan(const GlaArgs& a, cudaStream_t st);
 // y[t, h * vdim + :] (leading dimension ldy) = o[t, h, :] / sqrt(mean(o^2) + eps) * w * silu(g[t, h, :])   (w: fp32 [vdim], shared by the heads)
@@ -117,17 +117,16 @@ int gla_out_gate(const float* o, const void* g, int ldg, const float* w, float e
 // over the token's concatenated heads with w [heads * vdim] (joint = true); the gate is silu(g) or sigmoid(g); the result
 // is multiplied by out_scale before it is rounded to the storage type.
 enum GateAct { GATE_SILU = 0, GATE_SIGMOID = 1 };
-// Per-head form only: o_stride (0: vdim) is the distance between two heads' rows of o; w_full = true reads the weight as
-// [heads * vdim] (every head its own) instead of [vdim]; with den_floor (fp32 [T, heads]) a head's row holds vdim outputs
-// and, behind them, the normaliser product n . q, and the outputs are divided by max(|n . q|, den_floor[t, h]) + den_eps
-// before the norm.
+// Per-head form only: w_full = true reads the weight as [heads * vdim] (every head its own) instead of [vdim]; with den_nq
+// and den_floor (fp32 [T, heads]) the outputs of head h are divided by max(|den_nq[t, h]|, den_floor[t, h]) + den_eps
+// before the norm (a normalised recurrence: den_nq is the product n . q of its running key sum with the query).
 struct OutGateArgs {
   const float* o; const void* g; int ldg; const float* w; float eps;
   void* y; int ldy; DType t;
   int T, heads, vdim;
   bool joint; int gate_act; float out_scale;
-  int o_stride = 0; bool w_full = false;
-  const float* den_floor = nullptr; float den_eps = 0.f;
+  bool w_full = false;
+  const float* den_nq = nullptr; const float* den_floor = nullptr; float den_eps = 0.f;
 };
 int recurrent_out_gate(const OutGateArgs& a, cudaStream_t st);
 // The scalar gates of the matrix-memory recurrence with exponential gating (mLSTM), per token and head, in fp32:

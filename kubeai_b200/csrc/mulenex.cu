@@ -79,8 +79,9 @@ struct LayerWeights {
   void* sh_in = nullptr;    // [n_sh, width]: gate [sff] | up [sff]
   void* sh_down = nullptr;  // [width, sff]
   void* cache = nullptr;    // attention: [num_blocks * page][kv_heads * (dim + vdim)]
-  float* state = nullptr;   // mlstm: [slots][heads][dim][vdim + 1]  (the last column is the normaliser n)
-  float* mstate = nullptr;  // mlstm: [slots][heads]
+  float* state = nullptr;   // mlstm: [slots][heads][dim][vdim]
+  float* nstate = nullptr;  // mlstm: [slots][heads][dim], the normaliser
+  float* mstate = nullptr;  // mlstm: [slots][heads], the log-scale
   GemmPlan p_in, p_out, p_up, p_down, p_shin, p_shdown;
   std::vector<GemmPlan> p_egu, p_edown;
   CUtensorMap xm_out[kGemmNumBlockN], xm_ffh[kGemmNumBlockN], xm_shact[kGemmNumBlockN];
@@ -109,7 +110,7 @@ class Mulenex : public Model {
   float* x = nullptr;            // [Tcap][W]
   void *h = nullptr, *inb = nullptr, *ycat = nullptr, *ao = nullptr, *fo = nullptr, *hrow = nullptr, *vfirst = nullptr, *ffh = nullptr;
   void *egu = nullptr, *eact = nullptr, *sh = nullptr, *shact = nullptr, *sdown = nullptr;
-  float *qn = nullptr, *o32 = nullptr, *gpre = nullptr, *gkeep = nullptr, *gtake = nullptr, *gfloor = nullptr;
+  float *qn = nullptr, *o32 = nullptr, *gpre = nullptr, *gkeep = nullptr, *gtake = nullptr, *gfloor = nullptr, *gnq = nullptr;
   float *scores = nullptr, *topw = nullptr, *edown = nullptr, *logits = nullptr;
   int *topi = nullptr, *sorted_rows = nullptr, *tile_group = nullptr, *pair_pos = nullptr, *iota = nullptr;
   int row_cap = 0, moe_cap = 0, vfirst_ld = 0;
@@ -148,7 +149,7 @@ class Mulenex : public Model {
   size_t state_bytes_per_slot() const override {
     size_t b = 0;
     for (auto& s : spec)
-      if (s.mixer == MIX_MLSTM) b += (static_cast<size_t>(s.heads) * s.dim * (s.vdim + 1) + s.heads) * sizeof(float);
+      if (s.mixer == MIX_MLSTM) b += (static_cast<size_t>(s.heads) * s.dim * (s.vdim + 1) + s.heads) * sizeof(float);   // C, n, m
     return b;
   }
   // every attention layer sees the whole sequence: no page is ever behind all windows
@@ -275,7 +276,7 @@ class Mulenex : public Model {
       max_in = std::max(max_in, s.n_in);
       max_kout = std::max(max_kout, s.k_out);
       if (s.mixer == MIX_ATTENTION) max_qn = std::max(max_qn, s.heads * s.dim);
-      else { any_mlstm = true; max_o = std::max(max_o, s.heads * (s.vdim + 1)); max_h = std::max(max_h, s.heads); }
+      else { any_mlstm = true; max_o = std::max(max_o, s.heads * s.vdim); max_h = std::max(max_h, s.heads); }
       if (s.v_first) vfirst_ld = up8(s.kv_heads * s.vdim);
       if (s.mlp == MLP_DENSE) { any_dense = true; max_ff = std::max(max_ff, s.ff); }
       if (s.mlp == MLP_MOE) {
@@ -298,7 +299,8 @@ class Mulenex : public Model {
         rc |= dalloc(&w.cache, static_cast<size_t>(e.num_blocks) * e.page * s.kv_heads * (s.dim + s.vdim) * es);
       } else {
         rc |= mat(&w.w_gates, 2 * s.heads, W) | vec(&w.b_gates, 2 * s.heads) | vec(&w.h_norm, static_cast<size_t>(s.heads) * s.vdim);
-        rc |= dalloc(&w.state, static_cast<size_t>(e.num_slots) * s.heads * s.dim * (s.vdim + 1) * sizeof(float));
+        rc |= dalloc(&w.state, static_cast<size_t>(e.num_slots) * s.heads * s.dim * s.vdim * sizeof(float));
+        rc |= dalloc(&w.nstate, static_cast<size_t>(e.num_slots) * s.heads * s.dim * sizeof(float));
         rc |= dalloc(&w.mstate, static_cast<size_t>(e.num_slots) * s.heads * sizeof(float));
       }
       if (s.mlp != MLP_NONE) rc |= vec(&w.norm2, W) | vec(&w.norm2b, W);
@@ -318,7 +320,7 @@ class Mulenex : public Model {
     if (vfirst_ld) rc |= mat(&vfirst, T, vfirst_ld);
     if (any_mlstm)
       rc |= dalloc(&o32, T * max_o * sizeof(float)) | dalloc(&gpre, T * 2 * max_h * sizeof(float)) | dalloc(&gkeep, T * max_h * sizeof(float)) |
-            dalloc(&gtake, T * max_h * sizeof(float)) | dalloc(&gfloor, T * max_h * sizeof(float));
+            dalloc(&gtake, T * max_h * sizeof(float)) | dalloc(&gfloor, T * max_h * sizeof(float)) | dalloc(&gnq, T * max_h * sizeof(float));
     if (any_dense) rc |= mat(&ffh, T, max_ff);
     if (any_dense || any_moe) rc |= mat(&fo, T, W);
     if (any_moe) {
@@ -660,13 +662,13 @@ class Mulenex : public Model {
     g.z = nullptr; g.z_bias = nullptr; g.inv_tau = 1.f; g.q_scale = 1.0f / sqrtf(static_cast<float>(s.dim)); g.T = b.T;
     g.states = w.state; g.seqs = b.seqs; g.nseq = b.nseq;
     g.heads = s.heads; g.dim = s.dim; g.vdim = s.vdim; g.o = o32;
-    g.tok_decay = gkeep; g.tok_kscale = gtake; g.ones_col = 1;
+    g.tok_decay = gkeep; g.tok_kscale = gtake; g.nstate = w.nstate; g.nq = gnq;
     KRN("mlstm_scan", gla_scan(g, st));
     OutGateArgs og;
     og.o = o32; og.g = col(inb, s.off_g); og.ldg = s.n_in; og.w = w.h_norm; og.eps = eps;
     og.y = ycat; og.ldy = s.k_out; og.t = dt; og.T = b.T; og.heads = s.heads; og.vdim = s.vdim;
     og.joint = false; og.gate_act = GATE_SIGMOID; og.out_scale = 1.f;
-    og.o_stride = s.vdim + 1; og.w_full = true; og.den_floor = gfloor; og.den_eps = 1e-6f;
+    og.w_full = true; og.den_nq = gnq; og.den_floor = gfloor; og.den_eps = 1e-6f;
     KRN("mlstm_out_gate", recurrent_out_gate(og, st));
     return rc;
   }

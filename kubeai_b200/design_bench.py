@@ -1,7 +1,7 @@
 """Prefill and decode throughput of a registered design beside the closest existing model at equal width, depth, head
 and feed-forward sizes, on random weights (`bench.py --design nomanex`: beside the built-in Llama model;
 `bench.py --design zinavik`: beside Nomanex, whose recurrent scan, windowed attention and routed experts are the like
-kernels).  Every number is CUDA-event time of the engine's
+kernels; `bench.py --design mulenex`: beside Zinavik, which runs the same attention, scan, routing and projection kernels).  Every number is CUDA-event time of the engine's
 own step (b200_feed_step: the same packing, page pool, state slots and kernels as a scheduled step), after warm-up
 steps, with a buffer larger than L2 written between timed steps.  Per-kernel times come from a separate pass in which
 each launch is bracketed by events (b200_engine_profile_kernels for the design, b200_engine_profile_range for Llama),
@@ -44,6 +44,17 @@ def zinavik_config(z):
     ly = dict(type="parallel", mixer=dict(left=lf, right=rt, left_scale=1.0, right_scale=1.0), mlp=mo)
     return dict(architecture="Zinavik", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-5), embedding=dict(scale=1.0), streams=2,
                 layers=[ly, ly, ly, ly])
+
+
+def mulenex_config(z):
+    H = z["heads"]
+    at = dict(heads=H, kv_heads=max(1, H // 4), dim=DIM, vdim=VDIM, scale=DIM ** -0.5, softcap=30.0, q_temp=dict(coef=0.1, every=256), v_mix=True)
+    ml = dict(heads=H, dim=DIM, vdim=VDIM, gate_cap=15.0)
+    mo = dict(kind="moe", expert=dict(ff=z["eff"]), router=dict(experts=z["experts"], top=z["top"]), shared=dict(ff=z["eff"]))
+    dn = dict(kind="dense", ff=z["ff"])
+    layers = [dict(type="attention", mixer=at, mlp=mo), dict(type="mlstm", mixer=ml, mlp=mo),
+              dict(type="attention", mixer=at, mlp=dn), dict(type="mlstm", mixer=ml, mlp=mo)]
+    return dict(architecture="Mulenex", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-5), layers=layers)
 
 
 def flush_l2(torch, buf):
@@ -126,6 +137,35 @@ def run_design(cfgj, lim, z, batch, prompt, decode_steps, warmup, peaks, torch, 
                     "residual_norm_prefill_frac_of_hbm": nl * T * W * (4 + 4 + 2 + 2 + 2) / us(kp, "residual_norm") / (hbm * 1e9),
                     "moe_experts_prefill_frac_of_bf16_peak": 2.0 * 2 * T * z["top"] * 2 * W * z["eff"] / (us(kp, "moe_up") + us(kp, "moe_down")) / (tf * 1e12),
                 }
+            elif cfgj["architecture"] == "Mulenex":
+                att = [ly for ly in cfgj["layers"] if ly["type"] == "attention"]
+                rec = [ly for ly in cfgj["layers"] if ly["type"] == "mlstm"]
+                G = att[0]["mixer"]["kv_heads"]
+                keys = sum(p + 1 for p in range(prompt)) * batch
+                att_flops = 2.0 * len(att) * H * keys * (DIM + VDIM)
+                scan_flops = 2.0 * 3 * len(rec) * T * H * DIM * (VDIM + 1)
+                n_in = len(att) * (H * DIM + G * DIM + G * VDIM + 8) + len(rec) * (2 * H * DIM + 2 * H * VDIM)
+                k_out = len(cfgj["layers"]) * H * VDIM
+                proj_flops = 2.0 * T * W * (n_in + k_out)
+                state_bytes = 2.0 * len(rec) * batch * H * DIM * (VDIM + 1) * 4
+                dkeys = batch * (prompt + 1)
+                calls = 2 * len(cfgj["layers"]) + 1      # one boundary per sublayer, the last write-back alone
+                moes = sum(1 for ly in cfgj["layers"] if ly["mlp"] and ly["mlp"]["kind"] == "moe")
+                r["roofline"] = {
+                    "attention_prefill_frac_of_bf16_peak": att_flops / us(kp, "attention") / (tf * 1e12),
+                    "mlstm_scan_prefill_tflops": scan_flops / us(kp, "mlstm_scan") / 1e12,
+                    "projections_prefill_frac_of_bf16_peak": proj_flops / (us(kp, "proj_in") + us(kp, "proj_out")) / (tf * 1e12),
+                    "mlstm_scan_decode_frac_of_hbm": state_bytes / us(kd, "mlstm_scan") / (hbm * 1e9),
+                    "attention_decode_frac_of_hbm": len(att) * dkeys * G * (DIM + VDIM) * 2.0 / us(kd, "attention") / (hbm * 1e9),
+                    "projections_decode_frac_of_hbm": 2.0 * W * (n_in + k_out) / (us(kd, "proj_in") + us(kd, "proj_out")) / (hbm * 1e9),
+                    # boundary: reads and writes the fp32 residual, reads a bf16 sublayer output, writes a bf16 row
+                    "residual_norm_prefill_frac_of_hbm": calls * T * W * (8.0 + 2 + 2) / us(kp, "residual_norm") / (hbm * 1e9),
+                    "moe_experts_prefill_frac_of_bf16_peak": 2.0 * moes * T * z["top"] * 3 * W * z["eff"] / (us(kp, "moe_up") + us(kp, "moe_down")) / (tf * 1e12),
+                    "dense_ff_prefill_frac_of_bf16_peak": 2.0 * T * 2 * W * z["ff"] / (us(kp, "ff_up") + us(kp, "ff_down")) / (tf * 1e12),
+                    # gate chain, out gate: the small kernels around the scan, as time beside the scan's
+                    "mlstm_gates_prefill_us": us(kp, "mlstm_gates") * 1e6 + us(kp, "mlstm_gate_proj") * 1e6,
+                    "mlstm_out_gate_prefill_frac_of_hbm": len(rec) * T * H * ((VDIM + 1) * 4.0 + VDIM * 2 + VDIM * 2) / us(kp, "mlstm_out_gate") / (hbm * 1e9),
+                }
             else:
                 L = len(cfgj["layers"])
                 lf = cfgj["layers"][0]["mixer"]["left"]
@@ -163,6 +203,11 @@ def bench_size(design, name, z, batch, prompt, decode_steps, warmup, peaks):
     lim["num_kv_blocks"] = batch * ((lim["max_model_len"] + 15) // 16)
     res = {"size": dict(z, batch=batch, prompt=prompt)}
     T = batch * prompt
+    if design == "mulenex":
+        res["mulenex"] = run_design(mulenex_config(z), lim, z, batch, prompt, decode_steps, warmup, peaks, torch, buf)
+        res["zinavik"] = run_design(zinavik_config(z), lim, z, batch, prompt, decode_steps, warmup, peaks, torch, buf)
+        del buf
+        return res
     if design == "zinavik":
         res["zinavik"] = run_design(zinavik_config(z), lim, z, batch, prompt, decode_steps, warmup, peaks, torch, buf)
         res["nomanex"] = run_design(nomanex_config(z), lim, z, batch, prompt, decode_steps, warmup, peaks, torch, buf)
@@ -215,8 +260,8 @@ def _k_out(ly):
 
 
 def run(design, peaks, sizes=None, batch=8, prompt=512, decode_steps=8, warmup=3):
-    if design not in ("nomanex", "zinavik"):
-        raise SystemExit("unknown design %r (known: nomanex, zinavik)" % design)
+    if design not in ("nomanex", "zinavik", "mulenex"):
+        raise SystemExit("unknown design %r (known: nomanex, zinavik, mulenex)" % design)
     out = {"design": design, "dtype": "bf16", "data": "synthetic (seeded random weights and tokens)", "peaks": dict(hbm_gbs=peaks[0], bf16_tflops=peaks[1], source=peaks[2]),
            "timing": "CUDA events around the engine step, median of the timed steps, %d warm-up steps, 320 MB written between steps" % warmup,
            "sizes": {}}
