@@ -59,8 +59,8 @@ __global__ void gla_decay_kernel(float* z, const float* bias, int HD, float inv_
 // summed by the pass that writes the round's outputs.
 // MODE 0: learned per-channel decays, staged as a third row.  MODE 1: one constant decay per head (GlaArgs::head_decay): no
 // decay row is staged or read, the constant sits in a register.  MODE 2: one decay and one key scale per (token, head)
-// (GlaArgs::tok_decay / tok_kscale): the decays of a round's tokens sit in shared memory as G scalars, the key is scaled
-// as it is staged.
+// (GlaArgs::tok_decay / tok_kscale): both sit in shared memory as G scalars per round; the key scale multiplies the token's
+// value (and the normaliser's key) in the chain, (s k) v^T = k (s v)^T.
 // NRM (with MODE 2): the CTAs of the first column block also carry the normaliser n [dim] of the head, n <- decay n + k
 // (what the scan does to a state column whose value is 1).  The threads of a row slice share its rows (thread jj owns rows
 // jj, jj + tcols, ... of the slice, at most kNormRows of them); every thread leaves its part of n . q in shared memory, and
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
   const int ps = rpp + 4, Dp = P * ps;     // padded slice and row length
   float* vs = sm + static_cast<size_t>(G) * 3 * Dp;   // [G][cols]
   float* os = vs + G * cols;                          // [G][P][cols]
-  float* ds = os + G * P * cols;                      // [G] the round's decays (MODE 2)
+  float* ds = os + G * P * cols;                      // [2][G] the round's decays and key scales (MODE 2)
   // behind the decays: [G][threads] partial n . q (NRM)
   const bool nrm = NRM && blockIdx.x == 0;
   float nv[NRM ? NE : 1];
@@ -125,7 +125,6 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
           const T* rp = base + row * a.ld;
           float qv = ldf(rp + a.q_off + c), kv = ldf(rp + a.k_off + c);
           if (silu) { qv = siluf_(qv); kv = siluf_(kv); }
-          if (MODE == 2) kv *= __ldg(a.tok_kscale + row * a.heads + head);
           s3[(tt * 3) * Dp] = qv * a.q_scale;
           s3[(tt * 3 + 1) * Dp] = kv;
           if (!CD) s3[(tt * 3 + 2) * Dp] = __ldg(a.z + row * (a.heads * D) + c);
@@ -141,13 +140,21 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
       vs[e] = vv;
     }
     if (MODE == 2)
-      for (int tt = threadIdx.x; tt < gn; tt += kThreads) ds[tt] = __ldg(a.tok_decay + static_cast<long long>(tok0 + g0 + tt) * a.heads + head);
+      for (int tt = threadIdx.x; tt < gn; tt += kThreads) {
+        ds[tt] = __ldg(a.tok_decay + static_cast<long long>(tok0 + g0 + tt) * a.heads + head);
+        ds[G + tt] = __ldg(a.tok_kscale + static_cast<long long>(tok0 + g0 + tt) * a.heads + head);
+      }
     __syncthreads();
     for (int tt = 0; tt < gn; ++tt) {
       const float decay = MODE == 2 ? ds[tt] : hdecay;
+      const float kscale = MODE == 2 ? ds[G + tt] : 1.f;   // the key's scalar gate multiplies the value instead: (s k) v = k (s v)
       float v[NC], o[NC][4];
 #pragma unroll
-      for (int c = 0; c < NC; ++c) { v[c] = vs[tt * cols + jj + c * tcols]; o[c][0] = o[c][1] = o[c][2] = o[c][3] = 0.f; }
+      for (int c = 0; c < NC; ++c) {
+        v[c] = vs[tt * cols + jj + c * tcols];
+        if (MODE == 2) v[c] *= kscale;
+        o[c][0] = o[c][1] = o[c][2] = o[c][3] = 0.f;
+      }
       const float4* q4 = reinterpret_cast<const float4*>(sm + (tt * 3) * Dp + part * ps);
       const float4* k4 = reinterpret_cast<const float4*>(sm + (tt * 3 + 1) * Dp + part * ps);
       const float4* a4 = reinterpret_cast<const float4*>(sm + (tt * 3 + 2) * Dp + part * ps);
@@ -175,11 +182,11 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
         for (int e = 0; e < NE; ++e) {
           const int r = jj + e * tcols;
           if (r < rpp) {
-            nv[e] = fmaf(decay, nv[e], ks[r]);
+            nv[e] = fmaf(decay, nv[e], ks[r] * kscale);
             nacc = fmaf(nv[e], qs[r], nacc);
           }
         }
-        (os + G * P * cols + G)[tt * kThreads + threadIdx.x] = nacc;   // summed over the threads by the output pass: no reduction inside the token chain
+        (os + G * P * cols + 2 * G)[tt * kThreads + threadIdx.x] = nacc;   // summed over the threads by the output pass: no reduction inside the token chain
       }
     }
     __syncthreads();
@@ -192,7 +199,7 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
     if (NRM && nrm)
       for (int tt = threadIdx.x >> 5; tt < gn; tt += kThreads / 32) {   // a warp per token: the threads' partial products in a fixed order
         const int lane = threadIdx.x & 31;
-        const float* pq = ds + G + tt * kThreads;
+        const float* pq = ds + 2 * G + tt * kThreads;
         float q = (pq[lane] + pq[lane + 32]) + (pq[lane + 64] + pq[lane + 96]);
         for (int sft = 16; sft > 0; sft >>= 1) q += __shfl_xor_sync(0xffffffffu, q, sft);
         if (lane == 0) a.nq[static_cast<long long>(tok0 + g0 + tt) * a.heads + head] = q;
@@ -357,7 +364,7 @@ int gla_scan(const GlaArgs& a, cudaStream_t st) {
   dim3 grid((a.vdim + cols - 1) / cols, a.heads, a.nseq);
   int G = kGroup;
   if (const char* e = getenv("B200_GLA_GROUP")) G = std::max(1, atoi(e));   // A/B knob: tokens staged per round
-  auto smem_for = [&](int g) { return static_cast<size_t>(g) * (3 * P * (rows_per_part + 4) + (1 + P) * cols + 1 + (a.nstate ? kThreads : 0)) * sizeof(float); };
+  auto smem_for = [&](int g) { return static_cast<size_t>(g) * (3 * P * (rows_per_part + 4) + (1 + P) * cols + 2 + (a.nstate ? kThreads : 0)) * sizeof(float); };
   while (G > 1 && smem_for(G) > 44 * 1024) G >>= 1;
   const size_t smem = smem_for(G);
   if (smem > 48 * 1024) return -1;
