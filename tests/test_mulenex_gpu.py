@@ -162,7 +162,8 @@ def test_bfloat16_large_step_takes_the_per_expert_path_and_agrees_with_the_group
     assert np.median(rel_err(big, grouped.astype(np.float64))) < 0.03
 
 
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim,cap", [(4, 1, 16, 16, 5.0), (2, 2, 32, 48, None), (6, 2, 64, 32, 20.0), (8, 4, 128, 128, 30.0), (3, 3, 16, 32, 1.5)])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,cap", [(4, 1, 16, 16, 5.0), (2, 2, 32, 48, None), (6, 2, 64, 32, 20.0), (8, 4, 128, 128, 30.0), (3, 3, 16, 32, 1.5),
+                                                           (4, 2, 48, 80, 10.0), (2, 1, 96, 112, None)])
 def test_bfloat16_tensor_core_attention_equals_the_general_kernel(tmp_path, monkeypatch, heads, kv_heads, dim, vdim, cap):
     """Head sizes that fit the mma fragments take the tensor-core kernel in steps that bring prompt portions: several key
     tiles per sequence, groups of 1 to 4 query heads per key head, capped and uncapped scores, one gate per head, portions
