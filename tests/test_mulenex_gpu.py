@@ -536,6 +536,46 @@ def test_preemption_recomputes_cache_and_state_from_the_start(mix):
         greedy_agrees(o, p, got)
 
 
+def test_chat_completion_through_the_serving_shell(tmp_path):
+    """The design behind the HTTP handler chain, stepped by the engine's own background loop: prompt rendering, submit,
+    continuous batching of two concurrent requests, greedy sampling, SSE framing; the tokens are the oracle's."""
+    import json
+    import threading
+    from kubeai_b200.engine import Engine, default_config
+    from kubeai_b200.server import Server, tokenize
+    V = 300
+    cfg, W, d = build(tmp_path, MIX, seed=51, vocab=V)
+    o = oracle_for(cfg, W)
+    lim = default_config(manual_step=0, enable_prefix_caching=0, max_num_seqs=4, max_batched_tokens=32, max_model_len=256, num_kv_blocks=64)
+    eng = Engine(lim, d, dtype="float32")
+    srv = Server([eng], model="mx", vocab=V, max_model_len=256)
+    try:
+        out = {}
+
+        def ask(i, text):
+            body = dict(model="mx", messages=[{"role": "user", "content": text}], max_tokens=5, temperature=0, stream=(i == 0))
+            out[i] = srv.handle("POST", "/openai/v1/chat/completions", json.dumps(body))
+
+        th = [threading.Thread(target=ask, args=(i, t)) for i, t in enumerate(["Hello there, how are you?", "Hi"])]
+        for t in th:
+            t.start()
+        for t in th:
+            t.join()
+        assert out[0].status == 200 and out[1].status == 200
+        ev = out[0].sse_events()
+        assert ev[-1] == "[DONE]"
+        text0 = "".join(json.loads(e)["choices"][0]["delta"].get("content", "") for e in ev[:-1] if json.loads(e)["choices"])
+        text1 = out[1].json()["choices"][0]["message"]["content"]
+        for text, user in ((text0, "Hello there, how are you?"), (text1, "Hi")):
+            prompt = srv.render_prompt("/v1/chat/completions", json.dumps(dict(model="mx", messages=[{"role": "user", "content": user}])))
+            got = tokenize(text, V)
+            assert len(got) == 5
+            greedy_agrees(o, prompt, got)
+    finally:
+        srv.close()
+        eng.close()
+
+
 def test_a_checkpoint_without_a_tensor_the_config_asks_for_is_refused(tmp_path):
     from kubeai_b200 import B200Error
     from kubeai_b200.engine import Engine, default_config
