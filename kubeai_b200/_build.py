@@ -32,9 +32,11 @@ SOURCES = [
     "moe.cu",
     "hyper.cu",
     "window_attention.cu",
+    "ssm.cu",
     "nomanex.cu",
     "zinavik.cu",
     "mulenex.cu",
+    "nagilix.cu",
     "model_registry.cc",
     "abi_ops.cu",
     "engine.cu",

@@ -643,6 +643,8 @@ int Engine::init_model(const b200_config& c, std::unique_ptr<Model> mdl) {
   L = H = Hq = Hkv = I = QKV = 0;
   V = model->vocab();
   cfg.vocab = V;
+  // a design with a position table cannot run a sequence past its last row
+  if (model->max_positions() > 0 && cfg.max_model_len > model->max_positions()) cfg.max_model_len = std::max(16, model->max_positions());
   if (c.max_model_len < 16 || c.max_num_seqs < 1 || c.max_batched_tokens < 16) {
     set_error("unsupported limits (max_model_len >= 16, max_num_seqs >= 1, max_batched_tokens >= 16)");
     return B200_ERR_INVALID;
@@ -662,7 +664,8 @@ int Engine::init_model(const b200_config& c, std::unique_ptr<Model> mdl) {
     CK(cudaMemGetInfo(&fr, &tot));
     const float frac = cfg.kv_fraction > 0 ? cfg.kv_fraction : 0.85f;
     // weights and activations are allocated after the pool is sized: leave them half of what is free
-    nblocks = per_block ? static_cast<int64_t>(static_cast<double>(fr) * frac * 0.5 / static_cast<double>(per_block)) : 0;
+    // a design without per-token caches keeps pages for the bookkeeping alone: as many as its sequences can name
+    nblocks = per_block ? static_cast<int64_t>(static_cast<double>(fr) * frac * 0.5 / static_cast<double>(per_block)) : INT64_MAX;
     nblocks = std::min<int64_t>(nblocks, static_cast<int64_t>(Scap) * ((cfg.max_model_len + kPage - 1) / kPage));
   }
   const int64_t need_blocks = (static_cast<int64_t>(cfg.max_model_len) + kPage - 1) / kPage;

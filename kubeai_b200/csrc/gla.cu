@@ -125,8 +125,18 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
           const T* rp = base + row * a.ld;
           float qv = ldf(rp + a.q_off + c), kv = ldf(rp + a.k_off + c);
           if (silu) { qv = siluf_(qv); kv = siluf_(kv); }
+          if (a.rope && i < a.rot_dims) {
+            // rotate-half layout: dimension i of the head is paired with i + rot_dims / 2
+            const int half = a.rot_dims >> 1;
+            const bool low = i < half;
+            const int cp = low ? c + half : c - half;
+            const float2 r = __ldg(a.rope + static_cast<long long>(pos0 + g0 + tt) * half + (low ? i : i - half));
+            const float qo = ldf(rp + a.q_off + cp), ko = ldf(rp + a.k_off + cp);
+            qv = low ? qv * r.x - qo * r.y : qv * r.x + qo * r.y;
+            kv = low ? kv * r.x - ko * r.y : kv * r.x + ko * r.y;
+          }
           s3[(tt * 3) * Dp] = qv * a.q_scale;
-          s3[(tt * 3 + 1) * Dp] = kv;
+          s3[(tt * 3 + 1) * Dp] = kv * a.k_scale;
           if (!CD) s3[(tt * 3 + 2) * Dp] = __ldg(a.z + row * (a.heads * D) + c);
         }
       } else {
@@ -262,7 +272,7 @@ __global__ void recurrent_out_gate_kernel(OutGateArgs a, long long units) {
   // a normalised recurrence: the head's outputs are divided by max(|n . q|, floor) + den_eps before the norm
   const long long th = t * a.heads + c0 / a.vdim;
   const float dinv = a.den_nq ? 1.0f / (fmaxf(fabsf(a.den_nq[th]), a.den_floor[th]) + a.den_eps) : 1.0f;
-  const float* w = a.w + (a.w_full ? c0 : 0);
+  const float* w = a.w ? a.w + (a.w_full ? c0 : 0) : nullptr;   // null: a norm without a weight
   const T* g = static_cast<const T*>(a.g) + t * a.ldg + c0;
   T* y = static_cast<T*>(a.y) + t * a.ldy + c0;
   float ss = 0.f;
@@ -279,7 +289,7 @@ __global__ void recurrent_out_gate_kernel(OutGateArgs a, long long units) {
     const float gv = ldf(g + i);
     const float sg = 1.0f / (1.0f + expf(-gv));
     const float gate = a.gate_act == GATE_SIGMOID ? sg : gv * sg;
-    stf(y + i, op[i] * dinv * inv * w[i] * gate * a.out_scale);
+    stf(y + i, op[i] * dinv * inv * (w ? w[i] : 1.0f) * gate * a.out_scale);
   }
 }
 
@@ -336,7 +346,7 @@ int mlstm_gates(const MlstmGateArgs& a, cudaStream_t st) {
 int recurrent_out_gate(const OutGateArgs& a, cudaStream_t st) {
   const long long units = a.joint ? a.T : static_cast<long long>(a.T) * a.heads;
   if (units <= 0) return 0;
-  if (!a.o || !a.g || !a.w || !a.y || a.heads < 1 || a.vdim < 1) return -1;
+  if (!a.o || !a.g || !a.y || a.heads < 1 || a.vdim < 1) return -1;
   if (a.joint && (a.w_full || a.den_nq)) return -1;
   if (a.den_nq && !a.den_floor) return -1;
   const int th = a.joint ? (a.heads * a.vdim >= 1024 ? 256 : 128) : 128;
@@ -349,6 +359,7 @@ int recurrent_out_gate(const OutGateArgs& a, cudaStream_t st) {
 int gla_scan(const GlaArgs& a, cudaStream_t st) {
   if (a.nseq <= 0) return 0;
   if (a.dim < 1 || a.vdim < 1 || a.heads < 1) return -1;
+  if (a.rope && (a.rot_dims < 2 || a.rot_dims % 2 || a.rot_dims > a.dim || a.act != GLA_ACT_NONE)) return -1;
   int P = 1;
   while (P * kRows < a.dim) P <<= 1;
   if (P > 32) return -1;   // dim <= 1024

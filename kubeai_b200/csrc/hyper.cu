@@ -8,6 +8,10 @@
 // writes the normed row in the storage type of the projections.  With one stream and no mixing weights the same kernel
 // is the ordinary pre-norm residual step x <- x + y; h = rmsnorm(x).  Everything is fp32 up to the single rounding of h.
 //
+// A gated write-back multiplies y by sigmoid(gate + bias), the gate being a projection of the sublayer's own input.
+// `embed_learned_pos` fills the streams with the token's embedding row plus a learned position row; `branch_norm_sum` is
+// the meeting point of two mixers that ran side by side, each RMS-normed over the width with its own weight.
+//
 // Beside it, for designs with one residual and a norm on BOTH sides of every sublayer (mixers.h SandwichArgs): the
 // sublayer's output is RMS-normed before it is added, x <- x + norm_post(y + bias), and the next sublayer reads
 // norm_pre(x); one kernel per boundary, a CTA per token row, two fixed-order reductions.  And the sinusoidal position
@@ -43,6 +47,14 @@ __global__ void embed_scaled_kernel(const TW* embed, const int* ids, float* x, i
   }
 }
 
+// the gate of a gated write-back: sigmoid(pre-activation + bias) of column i of token t, in fp32
+__device__ __forceinline__ float gate_at(const HyperArgs& a, long long t, int i) {
+  const long long at = t * a.ldg + i;
+  const float z = (a.tg == DT_BF16 ? __bfloat162float(static_cast<const bf16*>(a.gate)[at]) : static_cast<const float*>(a.gate)[at]) +
+                  (a.gate_bias ? a.gate_bias[i] : 0.f);
+  return 1.0f / (1.0f + expf(-z));
+}
+
 template <typename TY, typename TH>
 __global__ void hyper_step_kernel(HyperArgs a) {
   extern __shared__ float us[];   // [W] the sublayer input before the norm
@@ -68,7 +80,8 @@ __global__ void hyper_step_kernel(HyperArgs a) {
     for (int s = 0; s < kMaxStreams; ++s)
       if (s < n) xs[s] = a.x[s * a.stream_stride + t * a.W + i];
     if (y) {
-      const float yv = ldf(y + t * a.W + i);
+      float yv = ldf(y + t * a.W + i);
+      if (a.gate) yv *= gate_at(a, t, i);
       float nx[kMaxStreams];
 #pragma unroll
       for (int j = 0; j < kMaxStreams; ++j) {
@@ -158,7 +171,11 @@ __global__ void __launch_bounds__(256) hyper_step_vec_kernel(HyperArgs a) {
       if (s < n) { const float4 v = ld4(a.x + s * a.stream_stride + t * a.W + i); xs[s][0] = v.x; xs[s][1] = v.y; xs[s][2] = v.z; xs[s][3] = v.w; }
     if (y) {
       const float4 y4 = ld4(y + t * a.W + i);
-      const float yv[4] = {y4.x, y4.y, y4.z, y4.w};
+      float yv[4] = {y4.x, y4.y, y4.z, y4.w};
+      if (a.gate) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) yv[c] *= gate_at(a, t, i + c);
+      }
       float nx[kMaxStreams][4];
 #pragma unroll
       for (int j = 0; j < kMaxStreams; ++j) {
@@ -222,6 +239,45 @@ __global__ void __launch_bounds__(256) hyper_step_vec_kernel(HyperArgs a) {
     const float4 u = ld4(us + i), w = ld4(a.norm_w + i);
     st4(h + i, make_float4(u.x * inv * w.x, u.y * inv * w.y, u.z * inv * w.z, u.w * inv * w.w));
   }
+}
+
+template <typename TW>
+__global__ void embed_learned_pos_kernel(const TW* embed, const TW* pos_table, const int* ids, const int* pos, float* x, int W, int vocab, int max_pos,
+                                         int streams, long long stride) {
+  const long long t = blockIdx.x;
+  int id = ids[t], p = pos[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
+  const TW* e = embed + static_cast<long long>(id) * W;
+  const TW* pr = pos_table + static_cast<long long>(p) * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = ldf(e + i) + ldf(pr + i);
+    for (int s = 0; s < streams; ++s) x[s * stride + t * W + i] = v;
+  }
+}
+
+// one CTA per token: both branches' sums of squares in one pass (warps added in a fixed order), then the weighted sum
+template <typename T, typename TY>
+__global__ void __launch_bounds__(256) branch_norm_sum_kernel(BranchNormArgs a) {
+  __shared__ float red[2][8];
+  const long long t = blockIdx.x;
+  const T* pa = static_cast<const T*>(a.a) + t * a.W;
+  const T* pb = static_cast<const T*>(a.b) + t * a.W;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
+    const float va = ldf(pa + i), vb = ldf(pb + i);
+    sa = fmaf(va, va, sa);
+    sb = fmaf(vb, vb, sb);
+  }
+  for (int o = 16; o > 0; o >>= 1) { sa += __shfl_xor_sync(0xffffffffu, sa, o); sb += __shfl_xor_sync(0xffffffffu, sb, o); }
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
+  if (lane == 0) { red[0][wrp] = sa; red[1][wrp] = sb; }
+  __syncthreads();
+  float ta = 0.f, tb = 0.f;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) { ta += red[0][w]; tb += red[1][w]; }
+  const float ia = 1.0f / sqrtf(ta / static_cast<float>(a.W) + a.eps), ib = 1.0f / sqrtf(tb / static_cast<float>(a.W) + a.eps);
+  TY* y = static_cast<TY*>(a.y) + t * a.W;
+  for (int i = threadIdx.x; i < a.W; i += blockDim.x) stf(y + i, a.scale * (ldf(pa + i) * ia * a.wa[i] + ldf(pb + i) * ib * a.wb[i]));
 }
 
 inline int threads_for(int W) { return W >= 2048 ? 256 : (W >= 256 ? 128 : 64); }
@@ -370,10 +426,35 @@ int embed_scaled(const void* embed, DType tw, const int* ids, float* x, int T, i
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+int embed_learned_pos(const void* embed, const void* pos_table, DType tw, const int* ids, const int* pos, float* x, int T, int W, int vocab,
+                      int max_pos, int streams, long long stream_stride, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (!embed || !pos_table || W < 1 || streams < 1 || max_pos < 1) return -1;
+  if (tw == DT_BF16)
+    embed_learned_pos_kernel<bf16><<<T, threads_for(W), 0, st>>>(static_cast<const bf16*>(embed), static_cast<const bf16*>(pos_table), ids, pos, x, W, vocab,
+                                                                 max_pos, streams, stream_stride);
+  else
+    embed_learned_pos_kernel<float><<<T, threads_for(W), 0, st>>>(static_cast<const float*>(embed), static_cast<const float*>(pos_table), ids, pos, x, W, vocab,
+                                                                  max_pos, streams, stream_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int branch_norm_sum(const BranchNormArgs& a, cudaStream_t st) {
+  if (a.T <= 0) return 0;
+  if (!a.a || !a.b || !a.wa || !a.wb || !a.y || a.W < 1) return -1;
+  const int th = threads_for(a.W);
+#define BN(T_, TY_) branch_norm_sum_kernel<T_, TY_><<<a.T, th, 0, st>>>(a)
+  if (a.t == DT_BF16) { if (a.ty == DT_BF16) BN(bf16, bf16); else BN(bf16, float); }
+  else { if (a.ty == DT_BF16) BN(float, bf16); else BN(float, float); }
+#undef BN
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 int hyper_step(const HyperArgs& a, cudaStream_t st) {
   if (a.rows <= 0) return 0;
   if (!a.x || a.streams < 1 || a.streams > kMaxStreams || a.W < 1) return -1;
   if (a.y && a.row_index) return -1;   // an update of chosen rows only would leave the streams inconsistent
+  if (a.gate && (!a.y || a.ldg < a.W)) return -1;
   const size_t smem = a.h ? static_cast<size_t>(a.W) * sizeof(float) : 0;
   if (smem > 48 * 1024) return -1;
   // four columns per thread where every row start is 16-byte aligned

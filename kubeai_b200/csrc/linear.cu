@@ -272,6 +272,7 @@ __global__ void __launch_bounds__(256) linear_picked_rows_kernel(LinearArgs a, P
   const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
   const int n = blockIdx.x * 8 + wrp, r = blockIdx.y;
   if (n >= a.N) return;
+  if (p.group_limit > 0 && (p.groups[r] < 0 || p.groups[r] >= p.group_limit)) return;   // a choice without a weight matrix
   const long long src = p.src_rows ? p.src_rows[r] : r / p.src_div;
   const long long dst = p.dst_rows[r];
   const TX* x = static_cast<const TX*>(a.X) + src * a.ldx;

@@ -5,8 +5,9 @@
 // paged keys and values with grouped heads, a sliding window and kept first tokens, hyper-connections (several residual
 // streams read and written through small mixing weights) with RMS norm, expert routing (softmax or sigmoid scores,
 // optionally group-limited, or a softmax over the chosen logits), the matrix-memory recurrence with exponential gating
-// (mLSTM), a sinusoidal position embedding, a residual step with a norm on both sides of the sublayer, and the gated
-// activations they use.
+// (mLSTM), a sinusoidal position embedding, a residual step with a norm on both sides of the sublayer, a short causal
+// convolution over time with its carried inputs, the selective scan of Mamba, chunked visibility and a softmax sink for
+// the paged attention, a learned position embedding, two normed branches summed, and the gated activations they use.
 //
 // Storage type: every activation / weight matrix is either bf16 or fp32 (DType); the residual stream, recurrent
 // states, router scores, decays, softmax and norm statistics are always fp32.  All pointers are device pointers.
@@ -52,11 +53,14 @@ inline LinearArgs linear_args(const void* X, DType tx, const void* W, DType tw, 
 int linear(const LinearArgs& a, cudaStream_t st);
 // `rows` rows (a handful: the expert choices of a decode step), row r reading X row src_rows[r] (or r / src_div), writing Y row
 // dst_rows[r], with weight matrix W + groups[r] * wbs (row_scale[r] applies); a.T, a.batch, x_rows and tile_group are not used.
+// group_limit > 0: a row whose group is negative or >= group_limit has no weight matrix and is skipped (its output row is
+// not written): the choices of a router that are not matrices at all, such as identity experts.
 struct PickedRows {
   int rows;
   const int* src_rows; int src_div;
   const int* dst_rows;
   const int* groups;
+  int group_limit = 0;
 };
 int linear_picked_rows(const LinearArgs& a, const PickedRows& p, cudaStream_t st);
 
@@ -96,6 +100,9 @@ int argmax_f32(const float* logits, int* out, int S, int V, cudaStream_t st);
 // token); z, z_bias and head_decay are then unused.  With them, nstate (fp32 [slot][heads][dim]) and nq (fp32 [T, heads])
 // make the scan carry the running key sum n_t = d_t n_(t-1) + s_t k_t beside the state and write nq[t, h] = n_t . (q_t *
 // q_scale), which normalised recurrences divide by.
+// rope (optional, [position][rot_dims / 2] of (cos, sin)): the first rot_dims dimensions of every query and key head are
+// rotated by the token's position as they are read, dimension i paired with i + rot_dims / 2 (the rotate-half layout), in
+// fp32; k_scale multiplies the key after the rotation.
 enum GlaAct { GLA_ACT_NONE = 0, GLA_ACT_SILU = 1 };
 struct GlaArgs {
   const void* qkv; DType t; int ld, q_off, k_off, v_off;
@@ -108,6 +115,7 @@ struct GlaArgs {
   int act = GLA_ACT_NONE;
   const float* tok_decay = nullptr; const float* tok_kscale = nullptr;
   float* nstate = nullptr; float* nq = nullptr;
+  const float2* rope = nullptr; int rot_dims = 0; float k_scale = 1.f;
 };
 int gla_scan(const GlaArgs& a, cudaStream_t st);
 // y[t, h * vdim + :] (leading dimension ldy) = o[t, h, :] / sqrt(mean(o^2) + eps) * w * silu(g[t, h, :])   (w: fp32 [vdim], shared by the heads)
@@ -120,6 +128,7 @@ enum GateAct { GATE_SILU = 0, GATE_SIGMOID = 1 };
 // Per-head form only: w_full = true reads the weight as [heads * vdim] (every head its own) instead of [vdim]; with den_nq
 // and den_floor (fp32 [T, heads]) the outputs of head h are divided by max(|den_nq[t, h]|, den_floor[t, h]) + den_eps
 // before the norm (a normalised recurrence: den_nq is the product n . q of its running key sum with the query).
+// w may be null: a norm without a weight.
 struct OutGateArgs {
   const float* o; const void* g; int ldg; const float* w; float eps;
   void* y; int ldy; DType t;
@@ -200,12 +209,38 @@ struct QkPrepArgs {
   void* v_raw_out = nullptr; int ld_raw = 0;
 };
 int qk_rope_norm_cache(const QkPrepArgs& a, cudaStream_t st);
+// The preparation of an attention whose queries and keys pass a short causal convolution over time and whose values are
+// the convolved keys.  qk: [T, heads * dim | kv_heads * dim], neighbouring columns of one row-major buffer (the
+// projections).  Per token, in fp32: every channel is convolved with its taps (conv_w [channels, taps], the last tap is
+// the token's own; the taps - 1 inputs before a portion's first token come from conv_state [slot][taps - 1][channels],
+// zeros before the sequence's start; conv_w null: no convolution); the convolved keys are the values of the cache row;
+// the whole query row (all heads at once) and the whole key row are divided by their root mean square (eps inside the
+// root) and multiplied by q_norm_w [heads * dim] / k_norm_w [kv_heads * dim]; the first rot_dims dimensions of every head
+// are rotated by the token's position, dimension i paired with i + rot_dims / 2 (rotate-half layout; rope as
+// rope_table_yarn writes it); query head h is multiplied by q_head_scale[h] (optional: a temperature per head).
+// Queries go to qn (fp32 [T, heads * dim]), keys to the cache row [kv_heads * dim (keys) | kv_heads * dim (values)].
+// The carried inputs are written afterwards by short_conv_carry over the same columns.
+struct ConvQkPrepArgs {
+  const void* qk; int ld; DType t;
+  const float* conv_w; int taps; const float* conv_state;
+  const float* q_norm_w; const float* k_norm_w; float eps;
+  const float2* rope; int rot_dims;
+  const float* q_head_scale;
+  const int* positions; const int* slots; const int* seq_of_tok; const int* seqs;
+  float* qn; void* cache;
+  int T, heads, kv_heads, dim;
+};
+int conv_qk_prep(const ConvQkPrepArgs& a, cudaStream_t st);
 // Softmax attention of token t (position p of its sequence) over the cached keys j <= p with p - j < window or
 // j < keep_first (kept tokens stay at their own positions).  Query head h reads key/value head h / (heads / kv_heads).
 // score = qn . k * scale, softmax in fp32.  y[t, h * vdim + :] = out_scale * o * sigmoid(gate[t, h * vdim + :]) (gate of
 // type t with leading dimension ldg, may be null: no gate), rounded once to type t (leading dimension ldy).
 // softcap > 0: score <- softcap * tanh(score / softcap) after the scale.  gate_per_head: the gate holds one number per
 // (token, head), gate[t * ldg + h], instead of one per output column.
+// chunk > 0 replaces the sliding window by chunked visibility: the token at position p sees the keys j <= p of its own
+// chunk, floor(j / chunk) = floor(p / chunk), chunks counted from position 0 of the sequence (window is then unused;
+// keep_first still applies).  sink (optional, fp32 [heads]): the softmax denominator of head h also holds exp(sink[h]),
+// a score without a key or a value that is neither scaled nor capped and counts once.
 struct WindowAttnArgs {
   const float* qn; const void* cache; DType t;
   const int* positions; const int* seq_of_tok; const int* block_tables; int max_blocks, page;
@@ -214,8 +249,46 @@ struct WindowAttnArgs {
   int T, heads, kv_heads, dim, vdim, window, keep_first; float scale;
   const int* seqs; int nseq; int max_ctx;
   float softcap = 0.f; bool gate_per_head = false;
+  int chunk = 0; const float* sink = nullptr;
 };
 int window_attention(const WindowAttnArgs& a, cudaStream_t st);
+
+// ---------------------------------------------------------------- short causal convolution, selective scan (ssm.cu)
+// y[t, c] = act(bias[c] + sum_j w[c, j] * u[t - taps + 1 + j, c]) over the tokens of t's own sequence: the last tap is the
+// token's own input, inputs before a portion's first token come from state [slot][taps - 1][C] (fp32, oldest first) when
+// the portion starts past position 0, and are zeros before the sequence's start.  u: C columns of a row-major buffer of
+// type t (leading dimension ldu); w fp32 [C, taps]; bias fp32 [C] or null; y of type ty.  Computed in fp32.
+// short_conv_carry writes the state a step leaves behind (the last taps - 1 inputs of every sequence, older ones shifted
+// in from the old state when the portion is shorter); it runs after every kernel of the step that reads the old state.
+enum ConvAct { CONV_NONE = 0, CONV_SILU = 1 };
+struct ShortConvArgs {
+  const void* u; int ldu; DType t;
+  const float* w; const float* bias; int act;
+  void* y; int ldy; DType ty;
+  float* state;
+  const int* seq_of_tok; const int* seqs; int nseq;
+  int T, C, taps;
+};
+int short_conv(const ShortConvArgs& a, cudaStream_t st);
+int short_conv_carry(const ShortConvArgs& a, cudaStream_t st);
+// The selective scan of Mamba, per sequence, channel c and state index n, in fp32:
+//   d = softplus(dt[t, c]);  S[c, n] <- exp(d * A[c, n]) * S[c, n] + d * x[t, c] * B[t, n];
+//   y[t, c] = (sum_n S[c, n] * C[t, n] + D[c] * x[t, c]) * silu(z[t, c])
+// x, z: [T, inner] column blocks of type t (x after its convolution and activation, z the gate's pre-activation); dt: fp32
+// [T, inner] pre-activations of the step size (with their bias); bc: fp32 rows holding B at column b_off and C at c_off
+// ([state] each); A fp32 [inner, state] (negative); D fp32 [inner]; states fp32 [slot][inner][state], zero for a
+// sequence whose first position is 0 whatever its slot held.  Sequential in the token: the same operations in the same
+// order however a prompt is cut.
+struct SelectiveScanArgs {
+  const void* x; int ldx; const void* z; int ldz; DType t;
+  const float* dt; int lddt;
+  const float* bc; int ldbc, b_off, c_off;
+  const float* A; const float* D;
+  float* states; const int* seqs; int nseq;
+  void* y; int ldy;
+  int inner, state;
+};
+int selective_scan(const SelectiveScanArgs& a, cudaStream_t st);
 
 // ---------------------------------------------------------------- hyper-connections, RMS norm (hyper.cu)
 // x[s][t] = embed[ids[t]] * scale for every stream s (fp32; stream s starts at x + s * stream_stride).
@@ -233,8 +306,25 @@ struct HyperArgs {
   const float* norm_w; float eps;
   void* h; DType th;
   const int* row_index; int rows; int W;
+  // gated write-back (optional): y[t, i] is multiplied by sigmoid(gate[t * ldg + i] + gate_bias[i]) before it enters the
+  // streams (gate of type tg, pre-activations of a projection; gate_bias fp32, may be null)
+  const void* gate = nullptr; DType tg = DT_BF16; int ldg = 0; const float* gate_bias = nullptr;
 };
 int hyper_step(const HyperArgs& a, cudaStream_t st);
+// x[s][t] = embed[ids[t]] + pos_table[pos[t]] for every stream s (fp32): a learned position vector, not scaled.
+// pos_table: [max_pos, W] of type tw; a position at or past max_pos reads the last row.
+int embed_learned_pos(const void* embed, const void* pos_table, DType tw, const int* ids, const int* pos, float* x, int T, int W, int vocab,
+                      int max_pos, int streams, long long stream_stride, cudaStream_t st);
+// Two branches, each RMS-normed over the width with its own weight, summed: for t < T
+//   y[t] = scale * (a[t] / sqrt(mean(a[t]^2) + eps) * wa + b[t] / sqrt(mean(b[t]^2) + eps) * wb)
+// a, b: [T, W] of type t; wa, wb fp32 [W]; y of type ty; fp32 statistics, one rounding.
+struct BranchNormArgs {
+  const void* a; const void* b; DType t;
+  const float* wa; const float* wb; float eps, scale;
+  void* y; DType ty;
+  int T, W;
+};
+int branch_norm_sum(const BranchNormArgs& a, cudaStream_t st);
 
 // Sinusoidal positions added to the embedding: x[t] = embed[ids[t]] + s(pos[t]), where column c of s(p) belongs to the
 // pair i = c / 2 with angle p * base^(-2i/W) and carries its sine (c even) or cosine (c odd).  freq: [(W + 1) / 2] float2,
@@ -266,15 +356,19 @@ int sandwich_step(const SandwichArgs& a, cudaStream_t st);
 // logits only.
 enum MoeScore { MOE_SOFTMAX = 0, MOE_SIGMOID = 1, MOE_TOP_SOFTMAX = 2 };
 // ld: leading dimension of scores (0: E); columns past E are left alone (a design may keep other fp32 outputs there).
+// select_bias (optional, fp32 [E]; MOE_SOFTMAX and MOE_SIGMOID): experts (and groups) are ranked by score + select_bias,
+// the weights stay the scores themselves.
 int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st,
-              int score_fn = MOE_SOFTMAX, int ld = 0);
+              int score_fn = MOE_SOFTMAX, int ld = 0, const float* select_bias = nullptr);
 // Sort the T * top (token, choice) pairs by expert into 64-row tiles: sorted_rows[cap] = token of each sorted row or -1,
 // tile_group[cap / 64] = expert of each tile or -1, pair_pos[T * top] = sorted row of each pair.  cap >= T*top + E*64.
 // expert_rows (optional): [E][2] = {first sorted row, rows} of every expert.
 // topk_w with sorted_w (optional): sorted_w[cap] = the router weight of each sorted row (0 for padding), for designs that
 // scale an expert's input instead of its output.
+// matrices (0: E): experts at or above it have no weights (identity experts); their tiles are marked -1, so that the
+// grouped launches skip them, while their rows keep their places in the order.
 int moe_align(const int* topk_ids, int T, int top, int E, int* sorted_rows, int* tile_group, int* pair_pos, int cap, cudaStream_t st,
-              int* expert_rows = nullptr, const float* topk_w = nullptr, float* sorted_w = nullptr);
+              int* expert_rows = nullptr, const float* topk_w = nullptr, float* sorted_w = nullptr, int matrices = 0);
 // out[t] = sum_k topk_w[t, k] * y[pair_pos[t * top + k]]   (y [cap, W] fp32 or bf16, k ascending)
 int moe_combine(const void* y, DType ty, const int* pair_pos, const float* topk_w, void* out, DType t, int T, int top, int W, cudaStream_t st);
 // out[t] = sum_k w[t, k] * y[pair_pos[t * top + k]] + sigmoid(add_gate[t * ld_gate]) * add[t]: the routed experts plus a
@@ -282,6 +376,10 @@ int moe_combine(const void* y, DType ty, const int* pair_pos, const float* topk_
 // input); add ([T, W]) is of type t and may be null (no shared expert); add_gate is fp32 and may be null (gate 1).
 int moe_combine_add(const void* y, DType ty, const int* pair_pos, const float* topk_w, const void* add, const float* add_gate, int ld_gate,
                     void* out, DType t, int T, int top, int W, cudaStream_t st);
+// The same with identity experts: a choice topk_ids[t, k] >= matrices contributes w[t, k] * x[t] (the expert's input row
+// itself, x of type t) instead of a row of y, which is not read for it.
+int moe_combine_identity(const void* y, DType ty, const int* pair_pos, const float* topk_w, const int* topk_ids, int matrices, const void* x,
+                         void* out, DType t, int T, int top, int W, cudaStream_t st);
 // bf16 helpers of the per-expert tensor-core path: x rows in sorted order (negative source row -> zeros; with row_scale the
 // row is multiplied by row_scale[r] in fp32 and rounded once), max(p, 0)^2 in place
 int moe_gather_bf16(const void* x, const int* sorted_rows, void* out, int rows, int W, cudaStream_t st, const float* row_scale = nullptr);

@@ -63,6 +63,9 @@ class Model {
   virtual int cache_window() const { return 0; }
   // the first tokens of a sequence that stay visible to every later token whatever the window: their pages are not returned
   virtual int cache_keep_first() const { return 0; }
+  // the most positions a sequence may have (a learned position table has that many rows); 0 = no limit of the design's own.
+  // The engine lowers its max_model_len to it.
+  virtual int max_positions() const { return 0; }
   // allocate weights (unset), activations for env.Tcap tokens, caches for env.num_blocks pages, states for env.num_slots
   virtual int init(const ModelEnv& env) = 0;
   // sizes that only the checkpoint's tensor shapes give; called before init() when there is a checkpoint
@@ -110,5 +113,6 @@ Model* engine_model(b200_engine* e);
 std::unique_ptr<Model> make_nomanex(const JVal& config, DType dtype, std::string* err);
 std::unique_ptr<Model> make_zinavik(const JVal& config, DType dtype, std::string* err);
 std::unique_ptr<Model> make_mulenex(const JVal& config, DType dtype, std::string* err);
+std::unique_ptr<Model> make_nagilix(const JVal& config, DType dtype, std::string* err);
 
 }  // namespace b200

@@ -13,6 +13,7 @@ const Entry kModels[] = {
     {"Nomanex", make_nomanex},
     {"Zinavik", make_zinavik},
     {"Mulenex", make_mulenex},
+    {"Nagilix", make_nagilix},
 };
 }  // namespace
 

@@ -18,7 +18,8 @@ namespace {
 typedef __nv_bfloat16 bf16;
 
 // one warp per token; scores row in global memory is the scratch (chosen entries are overwritten with -1)
-__global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, int score_fn, int ld) {
+__global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, int score_fn, int ld,
+                                 const float* bias) {
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
   const int lane = threadIdx.x & 31;
@@ -40,16 +41,20 @@ __global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, in
     for (int e = lane; e < E; e += 32) s[e] *= inv;
   }
   __syncwarp();
+  // with a selection bias the experts are ranked by score + bias (a chosen entry, marked, ranks below everything) and
+  // weighted by the score itself
+  const float lowest = bias ? -FLT_MAX : none;
+  auto rank = [&](int e) { const float v = s[e]; return bias ? (v == none ? -FLT_MAX : v + bias[e]) : v; };
   const int per = E / groups;
   // keep the best groups: bit g of `kept` (lane-uniform); groups <= 64
   unsigned long long kept = 0;
   for (int r = 0; r < keep; ++r) {
-    float best = none;
+    float best = lowest;
     int bg = 0x7fffffff;
     for (int g = lane; g < groups; g += 32) {
       if (kept >> g & 1ull) continue;
-      float gm = none;
-      for (int e = g * per; e < (g + 1) * per; ++e) gm = fmaxf(gm, s[e]);
+      float gm = lowest;
+      for (int e = g * per; e < (g + 1) * per; ++e) gm = fmaxf(gm, rank(e));
       if (gm > best) { best = gm; bg = g; }
     }
     for (int o = 16; o > 0; o >>= 1) {
@@ -61,11 +66,11 @@ __global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, in
   }
   float first = 0.f, sum = 0.f;   // MOE_TOP_SOFTMAX: the largest chosen logit and the sum of exp(logit - first) over the chosen
   for (int k = 0; k < top; ++k) {
-    float best = none;
+    float best = lowest;
     int be = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
       if (!(kept >> (e / per) & 1ull)) continue;
-      const float v = s[e];
+      const float v = rank(e);
       if (v > best) { best = v; be = e; }
     }
     for (int o = 16; o > 0; o >>= 1) {
@@ -74,6 +79,7 @@ __global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, in
       if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
     }
     if (be == 0x7fffffff) { be = 0; best = 0.f; }
+    else if (bias) best = s[be];     // the weight is the score without the bias
     if (k == 0) first = best;
     sum += expf(best - first);
     if (lane == 0) {
@@ -94,7 +100,7 @@ __global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, in
 
 // single CTA: histogram, padded offsets, scatter
 __global__ void __launch_bounds__(1024) moe_align_kernel(const int* topk_ids, int pairs, int top, int E, int* sorted_rows, int* tile_group,
-                                                         int* pair_pos, int cap, int* expert_rows, const float* topk_w, float* sorted_w) {
+                                                         int* pair_pos, int cap, int* expert_rows, const float* topk_w, float* sorted_w, int matrices) {
   extern __shared__ int sh[];   // count[E], start[E + 1], fill[E]
   int* count = sh;
   int* start = sh + E;
@@ -111,7 +117,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* topk_ids, in
       start[e] = at;
       if (expert_rows) { expert_rows[2 * e] = at; expert_rows[2 * e + 1] = count[e]; }
       const int tiles = (count[e] + 63) / 64;
-      for (int i = 0; i < tiles; ++i) tile_group[at / 64 + i] = e;
+      for (int i = 0; i < tiles; ++i) tile_group[at / 64 + i] = e < matrices ? e : -1;   // an expert without matrices: its tiles are skipped
       at += tiles * 64;
     }
     start[E] = at;
@@ -129,16 +135,19 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* topk_ids, in
 __device__ __forceinline__ float ldy(const float* p) { return *p; }
 __device__ __forceinline__ float ldy(const bf16* p) { return __bfloat162float(*p); }
 
+// ids with matrices and x (optional): a choice at or above `matrices` is an identity expert, whose output is the token's
+// row of x itself; its row of y was never written and is not read.
 template <typename T, typename TYIN>
 __global__ void moe_combine_kernel(const TYIN* y, const int* pair_pos, const float* topk_w, T* out, int top, int W, const T* add = nullptr,
-                                   const float* add_gate = nullptr, int ld_gate = 0) {
+                                   const float* add_gate = nullptr, int ld_gate = 0, const int* ids = nullptr, int matrices = 0,
+                                   const T* x = nullptr) {
   const long long t = blockIdx.x;
   float gate = 1.f;
   if (add && add_gate) gate = 1.0f / (1.0f + expf(-add_gate[t * ld_gate]));
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
-      const float yv = ldy(y + static_cast<long long>(pair_pos[t * top + k]) * W + i);
+      const float yv = (ids && ids[t * top + k] >= matrices) ? ldy(x + t * W + i) : ldy(y + static_cast<long long>(pair_pos[t * top + k]) * W + i);
       acc = topk_w ? fmaf(topk_w[t * top + k], yv, acc) : acc + yv;
     }
     if (add) acc = fmaf(gate, ldy(add + t * W + i), acc);
@@ -149,20 +158,22 @@ __global__ void moe_combine_kernel(const TYIN* y, const int* pair_pos, const flo
 
 }  // namespace
 
-int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st, int score_fn, int ld) {
+int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st, int score_fn, int ld,
+              const float* select_bias) {
   if (T <= 0) return 0;
   if (E < 1 || groups < 1 || groups > 64 || E % groups || keep < 1 || keep > groups || top < 1 || top > keep * (E / groups)) return -1;
-  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(scores, topk_ids, topk_w, T, E, groups, keep, top, score_fn, ld > 0 ? ld : E);
+  if (select_bias && score_fn == MOE_TOP_SOFTMAX) return -1;
+  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(scores, topk_ids, topk_w, T, E, groups, keep, top, score_fn, ld > 0 ? ld : E, select_bias);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 int moe_align(const int* topk_ids, int T, int top, int E, int* sorted_rows, int* tile_group, int* pair_pos, int cap, cudaStream_t st,
-              int* expert_rows, const float* topk_w, float* sorted_w) {
+              int* expert_rows, const float* topk_w, float* sorted_w, int matrices) {
   if (T <= 0) return 0;
   if (cap % 64 || cap < T * top + E * 64 || (sorted_w && !topk_w)) return -1;
   const size_t smem = static_cast<size_t>(3 * E + 1) * sizeof(int);
   if (smem > 48 * 1024) return -1;
-  moe_align_kernel<<<1, 1024, smem, st>>>(topk_ids, T * top, top, E, sorted_rows, tile_group, pair_pos, cap, expert_rows, topk_w, sorted_w);
+  moe_align_kernel<<<1, 1024, smem, st>>>(topk_ids, T * top, top, E, sorted_rows, tile_group, pair_pos, cap, expert_rows, topk_w, sorted_w, matrices > 0 ? matrices : E);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -191,6 +202,23 @@ int moe_combine_add(const void* y, DType ty, const int* pair_pos, const float* t
   else
     moe_combine_kernel<float, float><<<T, th, 0, st>>>(static_cast<const float*>(y), pair_pos, topk_w, static_cast<float*>(out), top, W,
                                                          static_cast<const float*>(add), add_gate, ld_gate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int moe_combine_identity(const void* y, DType ty, const int* pair_pos, const float* topk_w, const int* topk_ids, int matrices, const void* x,
+                         void* out, DType t, int T, int top, int W, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (!y || !pair_pos || !topk_ids || !x || !out || top < 1 || matrices < 0 || (ty == DT_BF16 && t != DT_BF16)) return -1;
+  const int th = W >= 1024 ? 256 : 128;
+  if (ty == DT_BF16)
+    moe_combine_kernel<bf16, bf16><<<T, th, 0, st>>>(static_cast<const bf16*>(y), pair_pos, topk_w, static_cast<bf16*>(out), top, W, nullptr, nullptr, 0,
+                                                       topk_ids, matrices, static_cast<const bf16*>(x));
+  else if (t == DT_BF16)
+    moe_combine_kernel<bf16, float><<<T, th, 0, st>>>(static_cast<const float*>(y), pair_pos, topk_w, static_cast<bf16*>(out), top, W, nullptr, nullptr, 0,
+                                                        topk_ids, matrices, static_cast<const bf16*>(x));
+  else
+    moe_combine_kernel<float, float><<<T, th, 0, st>>>(static_cast<const float*>(y), pair_pos, topk_w, static_cast<float*>(out), top, W, nullptr, nullptr, 0,
+                                                         topk_ids, matrices, static_cast<const float*>(x));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -2,7 +2,10 @@
 // (mixers.h WindowAttnArgs), with the preparation in front of it: interleaved rotary positions under YaRN-style
 // frequency scaling and a unit-RMS norm of every query and key head, optionally with a weight, a position-dependent query
 // gain and a blend of the values with an earlier layer's (QkPrepArgs).  Scores may be tanh-capped, the sigmoid output
-// gate is per output column or per head.
+// gate is per output column or per head.  A second preparation (ConvQkPrepArgs) serves attention whose queries and keys
+// pass a short causal convolution, a norm over the whole projection and a rotate-half rotation, and whose values are the
+// convolved keys.  Visibility may be chunked instead of windowed (the first visible key is the start of the token's
+// chunk), and the softmax may have a sink, a learned score per head in the denominator that has no key and no value.
 //
 // Visibility of key j for the token at position p: j <= p and (p - j < window or j < keep_first).  The visible keys of
 // a token are therefore two runs, [0, min(keep_first, lo)) and [lo, p] with lo = max(0, p - window + 1); both kernels
@@ -109,6 +112,75 @@ __global__ void __launch_bounds__(128) qk_prep_kernel(QkPrepArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------- convolved queries and keys
+// One CTA per token (ConvQkPrepArgs).  Pass 1: a thread per channel convolves the projections over time (its taps come
+// from the step's own rows or from the sequence's carried inputs), leaves the result in shared memory, writes the
+// convolved keys as the values of the cache row and adds to the sum of squares of the query row or of the key row; the two
+// sums meet in shared memory in warp order.  Pass 2: a thread per channel normalises its value and its rotation partner
+// over the WHOLE projection, applies the weights, rotates (dimension i with i + rot_dims / 2), applies the head's
+// temperature to queries and writes qn or the key part of the cache row.
+template <typename T>
+__global__ void __launch_bounds__(256) conv_qk_prep_kernel(ConvQkPrepArgs a) {
+  extern __shared__ float cv[];   // [(heads + kv_heads) * dim] convolved projections
+  __shared__ float red[2][8];
+  const long long t = blockIdx.x;
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int D = a.dim, HD = a.heads * D, GD = a.kv_heads * D, C = HD + GD;
+  const int p = a.positions[t];
+  const long long slot = a.slots[t];
+  const int* sq = a.seqs + a.seq_of_tok[t] * 8;
+  const int i0 = static_cast<int>(t) - sq[0];
+  const bool carried = sq[2] > 0;
+  const int taps = a.conv_w ? a.taps : 1;
+  const float* st = a.conv_state ? a.conv_state + static_cast<long long>(sq[3]) * (taps - 1) * C : nullptr;
+  const T* u = static_cast<const T*>(a.qk);
+  T* cache = static_cast<T*>(a.cache) + slot * (2ll * GD);
+  float ssq = 0.f, ssk = 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc;
+    if (a.conv_w) {
+      acc = 0.f;
+      for (int j = 0; j < taps; ++j) {
+        const int d = taps - 1 - j;
+        float v = 0.f;
+        if (i0 - d >= 0) v = ldf(u + (t - d) * a.ld + c);
+        else if (carried) v = st[static_cast<long long>(taps - 1 + i0 - d) * C + c];
+        acc = fmaf(a.conv_w[static_cast<long long>(c) * taps + j], v, acc);
+      }
+    } else {
+      acc = ldf(u + t * a.ld + c);
+    }
+    cv[c] = acc;
+    if (c < HD) ssq = fmaf(acc, acc, ssq);
+    else { ssk = fmaf(acc, acc, ssk); stf(cache + GD + (c - HD), acc); }
+  }
+  for (int o = 16; o > 0; o >>= 1) { ssq += __shfl_xor_sync(0xffffffffu, ssq, o); ssk += __shfl_xor_sync(0xffffffffu, ssk, o); }
+  if (lane == 0) { red[0][wrp] = ssq; red[1][wrp] = ssk; }
+  __syncthreads();
+  float tq = 0.f, tk = 0.f;
+  for (int w = 0; w < nw; ++w) { tq += red[0][w]; tk += red[1][w]; }
+  const float invq = 1.0f / sqrtf(tq / static_cast<float>(HD) + a.eps), invk = 1.0f / sqrtf(tk / static_cast<float>(GD) + a.eps);
+  const int half = a.rot_dims / 2;
+  const float2* cs = half ? a.rope + static_cast<long long>(p) * half : nullptr;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const bool isq = c < HD;
+    const int cc = isq ? c : c - HD;                // column within the query or the key row
+    const int hd = cc / D, i = cc - hd * D;
+    const float inv = isq ? invq : invk;
+    const float* nwt = isq ? a.q_norm_w : a.k_norm_w;
+    auto normed = [&](int col) { return cv[(isq ? 0 : HD) + col] * inv * (nwt ? nwt[col] : 1.0f); };
+    float v = normed(cc);
+    if (i < a.rot_dims) {
+      const int ih = i < half ? i : i - half;
+      const float2 r = cs[ih];
+      const float other = normed(hd * D + (i < half ? i + half : i - half));
+      v = i < half ? v * r.x - other * r.y : v * r.x + other * r.y;
+    }
+    if (isq) a.qn[t * HD + cc] = a.q_head_scale ? v * a.q_head_scale[hd] : v;
+    else stf(cache + cc, v);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- attention, any head size
 constexpr int kWarps = 4, kWarpsDecode = 16;
 constexpr int kMaxVR = 8;   // value columns per lane: vdim <= 256
@@ -149,7 +221,7 @@ __global__ void __launch_bounds__(kWarpsDecode * 32) window_attn_kernel(WindowAt
   const int g = h / (a.heads / a.kv_heads);
   const int p = a.positions[t];
   const int* bt = a.block_tables + static_cast<long long>(a.seq_of_tok[t]) * a.max_blocks;
-  const int lo = max(0, p - a.window + 1);
+  const int lo = a.chunk > 0 ? p / a.chunk * a.chunk : max(0, p - a.window + 1);   // first key of the token's chunk, or of its window
   const int nk = min(a.keep_first, lo);      // kept first tokens outside the window
   const int n = nk + (p - lo + 1);
   float* qs = sm;
@@ -204,9 +276,11 @@ __global__ void __launch_bounds__(kWarpsDecode * 32) window_attn_kernel(WindowAt
     if (c < Dv) mine[2 + c] = acc[r];
   }
   __syncthreads();
-  float mm = -FLT_MAX;
+  // the sink is one more score in the denominator: it has no key and no value, and is not scaled
+  const float sink = a.sink ? a.sink[h] : -FLT_MAX;
+  float mm = sink;
   for (int w = 0; w < nwarps; ++w) mm = fmaxf(mm, part[w * (Dv + 2)]);
-  float ll = 0.f;
+  float ll = a.sink ? expf(sink - mm) : 0.f;
   float f[kWarpsDecode];
 #pragma unroll
   for (int w = 0; w < kWarpsDecode; ++w) f[w] = 0.f;
@@ -304,7 +378,9 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
       *reinterpret_cast<uint32_t*>(Qs + r * LDK + c) = pack_bf16(v.x, v.y);
     }
   }
-  const int lo0 = max(0, p0 - a.window + 1);
+  // the first key a row at position p sees besides the kept first tokens: the start of its chunk, or of its window
+  auto first_key = [&](int p) { return a.chunk > 0 ? p / a.chunk * a.chunk : max(0, p - a.window + 1); };
+  const int lo0 = first_key(p0);
   const int nsink = min(a.keep_first, lo0);
   const int nst = (nsink + kTileKeys - 1) / kTileKeys;
   const int nwt = (p1 - lo0 + 1 + kTileKeys - 1) / kTileKeys;
@@ -353,12 +429,13 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
   for (int i = 0; i < NV; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   const int nv = Dv / 8;
   // this thread's two rows
-  int prow[2];
+  int prow[2], plo[2];
   bool rowok[2];
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
     const int r = 16 * wrp + g + 8 * hf, tq = r / gs;
     prow[hf] = p0 + tq;
+    plo[hf] = first_key(prow[hf]);
     rowok[hf] = tq < ntq;
   }
   lookup_rows(0);
@@ -366,6 +443,7 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
   // the positions of the warp's 16 rows, for the whole-tile test
   const int warp_pmin = p0 + (16 * wrp) / gs, warp_pmax = p0 + (16 * wrp + 15) / gs;
   const bool warp_ok = (16 * wrp + 15) / gs < ntq;
+  const int warp_lo = first_key(warp_pmax);   // the latest first key among the warp's rows
   // shared-memory addresses of this lane's ldmatrix rows, formed once: the loops below only add multiples of a k-step
   const uint32_t q_base = smem_u32(Qs + (16 * wrp + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + (lane >> 4) * 8);
   const uint32_t k_base = smem_u32(Ks + ((lane & 7) + (lane >> 4) * 8) * LDK + ((lane >> 3) & 1) * 8);
@@ -409,7 +487,7 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
         for (int e = 0; e < 4; ++e) sc[nt][e] = a.softcap * (1.0f - __fdividef(2.0f, __expf(sc[nt][e] * pre) + 1.0f));
     }
     const float sscale = a.softcap > 0.f ? 1.0f : a.scale;
-    const bool whole = cnt == kTileKeys && warp_ok && j0 + kTileKeys - 1 <= warp_pmin && (warp_pmax - j0 < a.window || j0 + kTileKeys <= a.keep_first);
+    const bool whole = cnt == kTileKeys && warp_ok && j0 + kTileKeys - 1 <= warp_pmin && (j0 >= warp_lo || j0 + kTileKeys <= a.keep_first);
     if (whole) {
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt)
@@ -425,7 +503,7 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int hf = e >> 1, col = nt * 8 + 2 * t4 + (e & 1), j = j0 + col, p = prow[hf];
-          const bool vis = rowok[hf] && col < cnt && j <= p && (p - j < a.window || j < a.keep_first);
+          const bool vis = rowok[hf] && col < cnt && j <= p && (j >= plo[hf] || j < a.keep_first);
           const float v = vis ? sc[nt][e] * sscale : kMasked;
           sc[nt][e] = v;
           mx[hf] = fmaxf(mx[hf], v);
@@ -487,7 +565,12 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
     const int r = 16 * wrp + g + 8 * hf, tq = r / gs, hh = r - tq * gs;
     const long long t = tok0 + tq;
     const int head = hy * gs + hh;
-    const float inv = 1.0f / ls;
+    float inv = 1.0f / ls;
+    if (a.sink) {
+      // one more score in the denominator, without a key or a value: move the reference point if the sink lies above it
+      const float sk = a.sink[head], mn = fmaxf(m[hf], sk), back = __expf(m[hf] - mn);
+      inv = back / (ls * back + __expf(sk - mn));
+    }
     bf16* y = static_cast<bf16*>(a.y) + t * a.ldy + static_cast<long long>(head) * Dv;
 #pragma unroll
     for (int i2 = 0; i2 < NV; ++i2) {
@@ -546,9 +629,28 @@ int qk_rope_norm_cache(const QkPrepArgs& a, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+int conv_qk_prep(const ConvQkPrepArgs& a, cudaStream_t st) {
+  if (a.T <= 0) return 0;
+  if (!a.qk || !a.qn || !a.cache || a.heads < 1 || a.kv_heads < 1 || a.dim < 1 || a.rot_dims < 0 || a.rot_dims > a.dim || a.rot_dims % 2 ||
+      (a.rot_dims && !a.rope) || (a.conv_w && (a.taps < 1 || (a.taps > 1 && !a.conv_state))) || !a.seqs || !a.seq_of_tok) return -1;
+  const int C = (a.heads + a.kv_heads) * a.dim;
+  const size_t smem = static_cast<size_t>(C) * sizeof(float);
+  static std::atomic<unsigned long long> set16{0}, set32{0};
+  if (smem > 200 * 1024) return -1;
+  const int th = C >= 2048 ? 256 : 128;
+  if (a.t == DT_BF16) {
+    if (smem > 48 * 1024 && !ensure_dynamic_smem(conv_qk_prep_kernel<bf16>, 200 * 1024, &set16)) return -2;
+    conv_qk_prep_kernel<bf16><<<a.T, th, smem, st>>>(a);
+  } else {
+    if (smem > 48 * 1024 && !ensure_dynamic_smem(conv_qk_prep_kernel<float>, 200 * 1024, &set32)) return -2;
+    conv_qk_prep_kernel<float><<<a.T, th, smem, st>>>(a);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 int window_attention(const WindowAttnArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
-  if (a.heads < 1 || a.kv_heads < 1 || a.heads % a.kv_heads || a.dim < 1 || a.vdim < 1 || a.vdim > 32 * kMaxVR || a.window < 1 || a.keep_first < 0 ||
+  if (a.heads < 1 || a.kv_heads < 1 || a.heads % a.kv_heads || a.dim < 1 || a.vdim < 1 || a.vdim > 32 * kMaxVR || (a.chunk <= 0 && a.window < 1) || a.keep_first < 0 ||
       a.page < 1) return -1;
   // Steps that bring portions of prompts take the tensor-core kernel when the head sizes fit its fragments; steps of
   // single tokens (and every fp32 model) take the general kernel.  B200_WATTN_MMA=0 / 1 forces the choice (A/B knob).
