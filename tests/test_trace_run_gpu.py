@@ -10,6 +10,7 @@ import numpy as np
 import pytest
 
 import mulenex_util as mx
+import nagilix_util as nx
 from zinavik_util import layer, left, make_config, moe, oracle_for, random_weights, rel_err, right, write_model_dir
 
 pytestmark = pytest.mark.gpu
@@ -57,8 +58,16 @@ def mulenex_model():
     return cfg, W, mx.oracle_for(cfg, W)
 
 
+def nagilix_model():
+    layers = [nx.parallel(l=nx.left(heads=6, kv_heads=3, dim=16, chunk=21, conv=4), r=nx.right(heads=2, dim=12, vdim=20), mlp=nx.moe(experts=3, identity=1, top=4, ff=24)),
+              nx.mamba(inner=48, state=8, dt_rank=4, mlp=None), nx.parallel(l=nx.left(heads=2, kv_heads=2, dim=8, chunk=50, rot_dims=4, conv=2), mlp=None)]
+    cfg = nx.make_config(layers, width=40, vocab=70, streams=3)
+    W = nx.random_weights(cfg, seed=95)
+    return cfg, W, nx.oracle_for(cfg, W)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("model", [zinavik_model, mulenex_model])
+@pytest.mark.parametrize("model", [zinavik_model, mulenex_model, nagilix_model])
 def test_replayed_schedule_gives_the_oracles_logits(tmp_path, dtype, model):
     cfg, W, o = model()
     d = write_model_dir(tmp_path / "m", cfg, W)
