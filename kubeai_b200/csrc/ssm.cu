@@ -13,7 +13,7 @@
 // to L neighbouring lanes (L a power of two, at most 32) that hold kPer state entries each in registers; a CTA walks one
 // sequence's tokens in rounds: all threads stage the round's B and C rows, step sizes, d x, x and z in shared memory
 // (coalesced over channels, softplus with log1pf / expf once per token and channel), the chain then touches shared memory
-// and registers only, and the round's outputs are finished and written by all threads.  The chain is sequential in the
+// and registers only (the decay exp(d A) is formed as 2^(d A log2 e) with A log2 e held in registers), and the round's outputs are finished and written by all threads.  The chain is sequential in the
 // token and does the same operations however the sequence was cut into steps.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -55,6 +55,89 @@ __global__ void short_conv_kernel(ShortConvArgs a) {
   }
   if (a.act == CONV_SILU) acc = siluf_(acc);
   stf(static_cast<TY*>(a.y) + t * a.ldy + c, acc);
+}
+
+// The same for rows whose starts are 16-byte aligned and up to four taps.
+template <int VEC> struct VecOf;
+template <> struct VecOf<8> { typedef bf16 type; };
+template <> struct VecOf<4> { typedef float type; };
+__device__ __forceinline__ void ldv(const bf16* p, float* v) {
+  const uint4 r = *reinterpret_cast<const uint4*>(p);
+  const uint32_t u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(u[i] << 16); v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+}
+__device__ __forceinline__ void ldv(const float* p, float* v) {
+  const float4 r = *reinterpret_cast<const float4*>(p);
+  v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+}
+__device__ __forceinline__ void stv(bf16* p, const float* v) {
+  uint32_t u[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]); u[i] = *reinterpret_cast<const uint32_t*>(&b); }
+  *reinterpret_cast<uint4*>(p) = make_uint4(u[0], u[1], u[2], u[3]);
+}
+__device__ __forceinline__ void stv(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+
+// A thread owns VEC neighbouring channels and walks TB consecutive token rows with the last TAPS - 1 inputs in registers:
+// every input row is loaded once, the weights of the thread's channels once per walk.  Where the walk enters another
+// sequence (or at its start) the window is filled again, from the rows before, the sequence's carried inputs or zeros.
+template <int VEC, int TAPS>
+__global__ void __launch_bounds__(128) short_conv_vec_kernel(ShortConvArgs a, int TB) {
+  typedef typename VecOf<VEC>::type T;
+  const int groups = a.C / VEC;
+  const int gi = blockIdx.x * blockDim.x + threadIdx.x;
+  if (gi >= groups) return;
+  const int c = gi * VEC;
+  const long long t0 = static_cast<long long>(blockIdx.y) * TB, t1 = min(static_cast<long long>(a.T), t0 + TB);
+  const T* u = static_cast<const T*>(a.u);
+  float w[TAPS][VEC], hist[TAPS > 1 ? TAPS - 1 : 1][VEC], bias[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    bias[e] = a.bias ? a.bias[c + e] : 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) w[j][e] = a.w[static_cast<long long>(c + e) * TAPS + j];
+  }
+  int cur = -1;
+  for (long long t = t0; t < t1; ++t) {
+    const int s = a.seq_of_tok[t];
+    if (s != cur) {
+      // hist[k] = the input TAPS - 1 - k tokens before t
+      cur = s;
+      const int* sq = a.seqs + s * 8;
+      const int i = static_cast<int>(t) - sq[0];
+      const bool carried = sq[2] > 0;
+      const float* st = a.state + static_cast<long long>(sq[3]) * (TAPS - 1) * a.C;
+#pragma unroll
+      for (int k = 0; k < TAPS - 1; ++k) {
+        const int d = TAPS - 1 - k;
+        if (i - d >= 0) ldv(u + (t - d) * a.ldu + c, hist[k]);
+        else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) hist[k][e] = carried ? st[static_cast<long long>(TAPS - 1 + i - d) * a.C + c + e] : 0.f;
+        }
+      }
+    }
+    float v[VEC], acc[VEC];
+    ldv(u + t * a.ldu + c, v);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      float r = bias[e];
+#pragma unroll
+      for (int k = 0; k < TAPS - 1; ++k) r = fmaf(w[k][e], hist[k][e], r);     // oldest tap first, the token's own last
+      r = fmaf(w[TAPS - 1][e], v[e], r);
+      acc[e] = a.act == CONV_SILU ? siluf_(r) : r;
+    }
+#pragma unroll
+    for (int k = 0; k + 1 < TAPS - 1; ++k)
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) hist[k][e] = hist[k + 1][e];
+    if (TAPS > 1) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) hist[TAPS - 2][e] = v[e];
+    }
+    stv(static_cast<T*>(a.y) + t * a.ldy + c, acc);
+  }
 }
 
 template <typename TU>
@@ -103,7 +186,7 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(SelectiveS
   for (int r = 0; r < kPer; ++r) {
     const int nn = part * kPer + r;
     const bool in = live && nn < a.state;
-    Ar[r] = in ? a.A[static_cast<long long>(c) * a.state + nn] : 0.f;
+    Ar[r] = in ? a.A[static_cast<long long>(c) * a.state + nn] * 1.44269504088896340736f : 0.f;   // A log2(e): exp(d A) = 2^(d A log2 e)
     S[r] = (in && pos0 > 0) ? Sg[nn] : 0.f;
   }
   const T* x = static_cast<const T*>(a.x);
@@ -136,7 +219,7 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(SelectiveS
       float acc = 0.f;
 #pragma unroll
       for (int r = 0; r < kPer; ++r) {
-        S[r] = fmaf(expf(d * Ar[r]), S[r], dx * Bt[r]);
+        S[r] = fmaf(exp2f(d * Ar[r]), S[r], dx * Bt[r]);
         acc = fmaf(S[r], Ct[r], acc);
       }
       for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -166,6 +249,20 @@ int short_conv(const ShortConvArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
   if (!a.u || !a.w || !a.y || a.C < 1 || a.taps < 1 || (a.taps > 1 && !a.state) || !a.seqs || !a.seq_of_tok) return -1;
   const long long total = static_cast<long long>(a.T) * a.C;
+  const int vec = a.t == DT_BF16 ? 8 : 4;
+  if (a.t == a.ty && a.taps >= 1 && a.taps <= 4 && a.C % vec == 0 && a.ldu % vec == 0 && a.ldy % vec == 0 && reinterpret_cast<uintptr_t>(a.u) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(a.y) % 16 == 0) {
+    // rows per walk: long enough to amortise the window's fill, short enough to leave every SM several CTAs
+    const int groups = a.C / vec;
+    int TB = 16;
+    while (TB > 1 && static_cast<long long>((a.T + TB - 1) / TB) * ((groups + 127) / 128) < 4 * 148) TB >>= 1;
+    dim3 vgrid((groups + 127) / 128, (a.T + TB - 1) / TB);
+#define SC(V_, K_) short_conv_vec_kernel<V_, K_><<<vgrid, 128, 0, st>>>(a, TB)
+    if (a.t == DT_BF16) { switch (a.taps) { case 1: SC(8, 1); break; case 2: SC(8, 2); break; case 3: SC(8, 3); break; default: SC(8, 4); } }
+    else { switch (a.taps) { case 1: SC(4, 1); break; case 2: SC(4, 2); break; case 3: SC(4, 3); break; default: SC(4, 4); } }
+#undef SC
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   const unsigned grid = static_cast<unsigned>((total + 255) / 256);
   if (a.t == DT_BF16) {
     if (a.ty == DT_BF16) short_conv_kernel<bf16, bf16><<<grid, 256, 0, st>>>(a);

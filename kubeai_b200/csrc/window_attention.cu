@@ -120,9 +120,9 @@ __global__ void __launch_bounds__(128) qk_prep_kernel(QkPrepArgs a) {
 // over the WHOLE projection, applies the weights, rotates (dimension i with i + rot_dims / 2), applies the head's
 // temperature to queries and writes qn or the key part of the cache row.
 template <typename T>
-__global__ void __launch_bounds__(256) conv_qk_prep_kernel(ConvQkPrepArgs a) {
+__global__ void __launch_bounds__(1024) conv_qk_prep_kernel(ConvQkPrepArgs a) {
   extern __shared__ float cv[];   // [(heads + kv_heads) * dim] convolved projections
-  __shared__ float red[2][8];
+  __shared__ float red[2][32];
   const long long t = blockIdx.x;
   const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int D = a.dim, HD = a.heads * D, GD = a.kv_heads * D, C = HD + GD;
@@ -637,7 +637,9 @@ int conv_qk_prep(const ConvQkPrepArgs& a, cudaStream_t st) {
   const size_t smem = static_cast<size_t>(C) * sizeof(float);
   static std::atomic<unsigned long long> set16{0}, set32{0};
   if (smem > 200 * 1024) return -1;
-  const int th = C >= 2048 ? 256 : 128;
+  // steps of few tokens leave most SMs idle, so a token's CTA is as wide as its row allows (a thread per channel up to the
+  // CTA's limit); steps of many tokens keep more CTAs per SM with narrower ones
+  const int th = a.T >= 256 ? (C >= 2048 ? 256 : 128) : std::min(1024, std::max(128, (C + 31) / 32 * 32));
   if (a.t == DT_BF16) {
     if (smem > 48 * 1024 && !ensure_dynamic_smem(conv_qk_prep_kernel<bf16>, 200 * 1024, &set16)) return -2;
     conv_qk_prep_kernel<bf16><<<a.T, th, smem, st>>>(a);

@@ -1,7 +1,9 @@
 """Prefill and decode throughput of a registered design beside the closest existing model at equal width, depth, head
 and feed-forward sizes, on random weights (`bench.py --design nomanex`: beside the built-in Llama model;
 `bench.py --design zinavik`: beside Nomanex, whose recurrent scan, windowed attention and routed experts are the like
-kernels; `bench.py --design mulenex`: beside Zinavik, which runs the same attention, scan, routing and projection kernels).  Every number is CUDA-event time of the engine's
+kernels; `bench.py --design mulenex`: beside Zinavik, which runs the same attention, scan, routing and projection kernels;
+`bench.py --design nagilix`: beside Zinavik, whose streams, paged attention, constant-decay scan and clamped routed experts
+are the like kernels).  Every number is CUDA-event time of the engine's
 own step (b200_feed_step: the same packing, page pool, state slots and kernels as a scheduled step), after warm-up
 steps, with a buffer larger than L2 written between timed steps.  Per-kernel times come from a separate pass in which
 each launch is bracketed by events (b200_engine_profile_kernels for the design, b200_engine_profile_range for Llama),
@@ -55,6 +57,17 @@ def mulenex_config(z):
     layers = [dict(type="attention", mixer=at, mlp=mo), dict(type="mlstm", mixer=ml, mlp=mo),
               dict(type="attention", mixer=at, mlp=dn), dict(type="mlstm", mixer=ml, mlp=mo)]
     return dict(architecture="Mulenex", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-5), layers=layers)
+
+
+def nagilix_config(z):
+    H, W = z["heads"], z["width"]
+    lf = dict(heads=H, kv_heads=max(1, H // 4), dim=DIM, vdim=DIM, conv=4, mask=dict(size=z["window"]), rot=dict(base=10000.0, dims=ROT), scale=DIM ** -0.5)
+    rt = dict(heads=H, dim=DIM, vdim=VDIM, decay=[1.0 - 2.0 ** -(5.0 + 5.0 * h / max(H - 1, 1)) for h in range(H)], rot=dict(base=10000.0, dims=DIM))
+    mo = dict(kind="moe", expert=dict(ff=z["eff"], limit=7.0), router=dict(experts=z["experts"], identity=2, top=z["top"]))
+    pa = dict(type="parallel", mixer=dict(left=lf, right=rt), mlp=mo)
+    ma = dict(type="mamba1", mixer=dict(inner=2 * W, state=16, dt_rank=W // 16, conv=4), mlp=mo)
+    return dict(architecture="Nagilix", vocab=z["vocab"], width=W, norm=dict(eps=1e-5), logit_scale=1.0, max_positions=4096, streams=2,
+                layers=[pa, ma, pa, ma])
 
 
 def flush_l2(torch, buf):
@@ -137,6 +150,44 @@ def run_design(cfgj, lim, z, batch, prompt, decode_steps, warmup, peaks, torch, 
                     "residual_norm_prefill_frac_of_hbm": nl * T * W * (4 + 4 + 2 + 2 + 2) / us(kp, "residual_norm") / (hbm * 1e9),
                     "moe_experts_prefill_frac_of_bf16_peak": 2.0 * 2 * T * z["top"] * 2 * W * z["eff"] / (us(kp, "moe_up") + us(kp, "moe_down")) / (tf * 1e12),
                 }
+            elif cfgj["architecture"] == "Nagilix":
+                par = [ly for ly in cfgj["layers"] if ly["type"] == "parallel"]
+                mam = [ly for ly in cfgj["layers"] if ly["type"] == "mamba1"]
+                L, Lp, Lm = len(cfgj["layers"]), len(par), len(mam)
+                lf, mm = par[0]["mixer"]["left"], mam[0]["mixer"]
+                G, ns, chunk = lf["kv_heads"], cfgj["streams"], lf["mask"]["size"]
+                I, N, R = mm["inner"], mm["state"], mm["dt_rank"]
+                keys = sum(p % chunk + 1 for p in range(prompt)) * batch
+                att_flops = 2.0 * Lp * H * keys * (DIM + DIM)
+                scan_flops = 2.0 * 3 * Lp * T * H * DIM * VDIM
+                n_in = Lp * (H * DIM + G * DIM + 2 * H * DIM + 2 * H * VDIM + W) + Lm * (2 * I + W)
+                k_out = Lp * (H * DIM + H * VDIM) + Lm * I
+                proj_flops = 2.0 * T * W * (n_in + k_out + L * W)       # the feed-forward's gate projection counts among them
+                pk = lambda k: us(k, "proj_in") + us(k, "proj_out") + us(k, "proj_gate")
+                dkeys = batch * (prompt % chunk + 1)
+                calls = 2 * L + 1
+                r["roofline"] = {
+                    "chunk_attention_prefill_frac_of_bf16_peak": att_flops / us(kp, "chunk_attention") / (tf * 1e12),
+                    "retention_scan_prefill_tflops": scan_flops / us(kp, "retention_scan") / 1e12,
+                    "projections_prefill_frac_of_bf16_peak": proj_flops / pk(kp) / (tf * 1e12),
+                    "retention_scan_decode_frac_of_hbm": 2.0 * Lp * batch * H * DIM * VDIM * 4 / us(kd, "retention_scan") / (hbm * 1e9),
+                    "chunk_attention_decode_frac_of_hbm": Lp * dkeys * G * 2 * DIM * 2.0 / us(kd, "chunk_attention") / (hbm * 1e9),
+                    "projections_decode_frac_of_hbm": 2.0 * W * (n_in + k_out + L * W) / pk(kd) / (hbm * 1e9),
+                    # stream boundary: reads and writes `ns` fp32 streams, reads a sublayer output and its gate row, writes a bf16 row
+                    "stream_norm_prefill_frac_of_hbm": calls * T * W * (8.0 * ns + 2 + 2 + 2) / us(kp, "stream_norm") / (hbm * 1e9),
+                    "moe_experts_prefill_frac_of_bf16_peak": 2.0 * L * T * z["top"] * 3 * W * z["eff"] / (us(kp, "moe_up") + us(kp, "moe_down")) / (tf * 1e12),
+                    # selective scan: per (token, channel, state) one exponential and two multiply-adds; the step reads x, z, the
+                    # fp32 step sizes and writes y; a decode step reads and writes every sequence's state once
+                    "selective_scan_prefill_gelem_s": Lm * T * I * N / us(kp, "selective_scan") / 1e9,
+                    "selective_scan_prefill_frac_of_hbm": Lm * T * I * (2 + 2 + 4 + 2.0) / us(kp, "selective_scan") / (hbm * 1e9),
+                    "selective_scan_decode_frac_of_hbm": 2.0 * Lm * batch * I * N * 4 / us(kd, "selective_scan") / (hbm * 1e9),
+                    # the preparation of the chunked attention: reads q | k rows (and taps - 1 rows before), writes fp32 queries and the cache row
+                    "conv_qk_prep_prefill_frac_of_hbm": Lp * T * ((H + G) * DIM * 2.0 + H * DIM * 4 + 2 * G * DIM * 2) / us(kp, "conv_qk_prep") / (hbm * 1e9),
+                    "short_conv_prefill_frac_of_hbm": Lm * T * I * (2.0 + 2) / us(kp, "short_conv") / (hbm * 1e9),
+                    "branch_norm_sum_prefill_frac_of_hbm": Lp * T * W * (2.0 + 2 + 4) / us(kp, "branch_norm_sum") / (hbm * 1e9),
+                    "retention_out_gate_prefill_frac_of_hbm": Lp * T * H * VDIM * (4.0 + 2 + 2) / us(kp, "retention_out_gate") / (hbm * 1e9),
+                    "ssm_thin_products_prefill_us": (us(kp, "ssm_x_proj") + us(kp, "ssm_dt_proj")) * 1e6,
+                }
             elif cfgj["architecture"] == "Mulenex":
                 att = [ly for ly in cfgj["layers"] if ly["type"] == "attention"]
                 rec = [ly for ly in cfgj["layers"] if ly["type"] == "mlstm"]
@@ -203,6 +254,11 @@ def bench_size(design, name, z, batch, prompt, decode_steps, warmup, peaks):
     lim["num_kv_blocks"] = batch * ((lim["max_model_len"] + 15) // 16)
     res = {"size": dict(z, batch=batch, prompt=prompt)}
     T = batch * prompt
+    if design == "nagilix":
+        res["nagilix"] = run_design(nagilix_config(z), lim, z, batch, prompt, decode_steps, warmup, peaks, torch, buf)
+        res["zinavik"] = run_design(zinavik_config(z), lim, z, batch, prompt, decode_steps, warmup, peaks, torch, buf)
+        del buf
+        return res
     if design == "mulenex":
         res["mulenex"] = run_design(mulenex_config(z), lim, z, batch, prompt, decode_steps, warmup, peaks, torch, buf)
         res["zinavik"] = run_design(zinavik_config(z), lim, z, batch, prompt, decode_steps, warmup, peaks, torch, buf)
@@ -260,8 +316,8 @@ def _k_out(ly):
 
 
 def run(design, peaks, sizes=None, batch=8, prompt=512, decode_steps=8, warmup=3):
-    if design not in ("nomanex", "zinavik", "mulenex"):
-        raise SystemExit("unknown design %r (known: nomanex, zinavik, mulenex)" % design)
+    if design not in ("nomanex", "zinavik", "mulenex", "nagilix"):
+        raise SystemExit("unknown design %r (known: nomanex, zinavik, mulenex, nagilix)" % design)
     out = {"design": design, "dtype": "bf16", "data": "synthetic (seeded random weights and tokens)", "peaks": dict(hbm_gbs=peaks[0], bf16_tflops=peaks[1], source=peaks[2]),
            "timing": "CUDA events around the engine step, median of the timed steps, %d warm-up steps, 320 MB written between steps" % warmup,
            "sizes": {}}
