@@ -18,6 +18,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include <algorithm>
 
@@ -91,7 +92,7 @@ __global__ void __launch_bounds__(128) short_conv_vec_kernel(ShortConvArgs a, in
   const int c = gi * VEC;
   const long long t0 = static_cast<long long>(blockIdx.y) * TB, t1 = min(static_cast<long long>(a.T), t0 + TB);
   const T* u = static_cast<const T*>(a.u);
-  float w[TAPS][VEC], hist[TAPS > 1 ? TAPS - 1 : 1][VEC], bias[VEC];
+  float w[TAPS][VEC], hist[TAPS > 1 ? TAPS - 1 : 1][VEC], bias[VEC], rows[4][VEC];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) {
     bias[e] = a.bias ? a.bias[c + e] : 0.f;
@@ -118,8 +119,16 @@ __global__ void __launch_bounds__(128) short_conv_vec_kernel(ShortConvArgs a, in
         }
       }
     }
+    // the loads of up to four rows are issued together, ahead of the arithmetic of the first
+    const int q = static_cast<int>(t - t0) & 3;
+    if (q == 0) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+        if (t + r < t1) ldv(u + (t + r) * a.ldu + c, rows[r]);
+    }
     float v[VEC], acc[VEC];
-    ldv(u + t * a.ldu + c, v);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) v[e] = q == 0 ? rows[0][e] : (q == 1 ? rows[1][e] : (q == 2 ? rows[2][e] : rows[3][e]));
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
       float r = bias[e];
@@ -161,10 +170,11 @@ __global__ void short_conv_carry_kernel(ShortConvArgs a) {
 }
 
 constexpr int kScanThreads = 128;
-constexpr int kPer = 8;        // state entries per lane
 constexpr int kRound = 16;     // tokens staged per round
 
-template <typename T>
+// kPer = state entries per lane: 8 where the step has threads enough to fill the GPU that way, 4 (twice the lanes per
+// channel, half the chain per lane) where it has not
+template <typename T, int kPer>
 __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(SelectiveScanArgs a, int L, int G) {
   extern __shared__ float sm[];
   const int chans = kScanThreads / L, NP = L * kPer;      // channels per CTA, padded state size
@@ -286,16 +296,23 @@ int short_conv_carry(const ShortConvArgs& a, cudaStream_t st) {
 int selective_scan(const SelectiveScanArgs& a, cudaStream_t st) {
   if (a.nseq <= 0) return 0;
   if (!a.x || !a.z || !a.dt || !a.bc || !a.A || !a.D || !a.states || !a.y || a.inner < 1 || a.state < 1) return -1;
-  int L = 1;
-  while (L * kPer < a.state) L <<= 1;
+  int sms = 148;
+  { int dev = 0; if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  auto lanes = [&](int per) { int l = 1; while (l * per < a.state) l <<= 1; return l; };
+  int per = 8;
+  if (lanes(8) > 32 || (lanes(4) <= 32 && static_cast<long long>(a.nseq) * a.inner * lanes(8) < static_cast<long long>(sms) * 1536)) per = 4;
+  if (const char* e = getenv("B200_SSM_PER")) per = atoi(e) == 4 ? 4 : 8;   // A/B knob
+  const int L = lanes(per);
   if (L > 32) return -1;   // state <= 256
   const int chans = kScanThreads / L;
   int G = kRound;
-  auto smem_for = [&](int g) { return static_cast<size_t>(g) * (2 * L * kPer + 5 * chans) * sizeof(float); };
+  auto smem_for = [&](int g) { return static_cast<size_t>(g) * (2 * L * per + 5 * chans) * sizeof(float); };
   while (G > 1 && smem_for(G) > 44 * 1024) G >>= 1;
   dim3 grid((a.inner + chans - 1) / chans, a.nseq);
-  if (a.t == DT_BF16) selective_scan_kernel<bf16><<<grid, kScanThreads, smem_for(G), st>>>(a, L, G);
-  else selective_scan_kernel<float><<<grid, kScanThreads, smem_for(G), st>>>(a, L, G);
+#define SS(T_, P_) selective_scan_kernel<T_, P_><<<grid, kScanThreads, smem_for(G), st>>>(a, L, G)
+  if (a.t == DT_BF16) { if (per == 4) SS(bf16, 4); else SS(bf16, 8); }
+  else { if (per == 4) SS(float, 4); else SS(float, 8); }
+#undef SS
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

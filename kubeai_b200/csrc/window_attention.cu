@@ -116,9 +116,9 @@ __global__ void __launch_bounds__(128) qk_prep_kernel(QkPrepArgs a) {
 // One CTA per token (ConvQkPrepArgs).  Pass 1: a thread per channel convolves the projections over time (its taps come
 // from the step's own rows or from the sequence's carried inputs), leaves the result in shared memory, writes the
 // convolved keys as the values of the cache row and adds to the sum of squares of the query row or of the key row; the two
-// sums meet in shared memory in warp order.  Pass 2: a thread per channel normalises its value and its rotation partner
-// over the WHOLE projection, applies the weights, rotates (dimension i with i + rot_dims / 2), applies the head's
-// temperature to queries and writes qn or the key part of the cache row.
+// sums meet in shared memory in warp order.  Pass 2: a thread per rotation pair (dimension i with i + rot_dims / 2) or
+// unrotated column normalises over the WHOLE projection, applies the weights, rotates, applies the head's temperature to
+// queries and writes qn or the key part of the cache row.
 template <typename T>
 __global__ void __launch_bounds__(1024) conv_qk_prep_kernel(ConvQkPrepArgs a) {
   extern __shared__ float cv[];   // [(heads + kv_heads) * dim] convolved projections
@@ -140,12 +140,19 @@ __global__ void __launch_bounds__(1024) conv_qk_prep_kernel(ConvQkPrepArgs a) {
     float acc;
     if (a.conv_w) {
       acc = 0.f;
-      for (int j = 0; j < taps; ++j) {
-        const int d = taps - 1 - j;
-        float v = 0.f;
-        if (i0 - d >= 0) v = ldf(u + (t - d) * a.ld + c);
-        else if (carried) v = st[static_cast<long long>(taps - 1 + i0 - d) * C + c];
-        acc = fmaf(a.conv_w[static_cast<long long>(c) * taps + j], v, acc);
+      const float* wc = a.conv_w + static_cast<long long>(c) * taps;
+      if (i0 >= taps - 1) {
+        // every tap lies in the step's own rows
+        const T* up = u + (t - (taps - 1)) * a.ld + c;
+        for (int j = 0; j < taps; ++j) acc = fmaf(wc[j], ldf(up + static_cast<long long>(j) * a.ld), acc);
+      } else {
+        for (int j = 0; j < taps; ++j) {
+          const int d = taps - 1 - j;
+          float v = 0.f;
+          if (i0 - d >= 0) v = ldf(u + (t - d) * a.ld + c);
+          else if (carried) v = st[static_cast<long long>(taps - 1 + i0 - d) * C + c];
+          acc = fmaf(wc[j], v, acc);
+        }
       }
     } else {
       acc = ldf(u + t * a.ld + c);
@@ -162,22 +169,28 @@ __global__ void __launch_bounds__(1024) conv_qk_prep_kernel(ConvQkPrepArgs a) {
   const float invq = 1.0f / sqrtf(tq / static_cast<float>(HD) + a.eps), invk = 1.0f / sqrtf(tk / static_cast<float>(GD) + a.eps);
   const int half = a.rot_dims / 2;
   const float2* cs = half ? a.rope + static_cast<long long>(p) * half : nullptr;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    const bool isq = c < HD;
-    const int cc = isq ? c : c - HD;                // column within the query or the key row
-    const int hd = cc / D, i = cc - hd * D;
+  // a thread takes an item of a head: a rotation pair (columns i and i + half, both outputs) or a column past the rotated ones
+  const int per_head = D - half, items = (a.heads + a.kv_heads) * per_head;
+  for (int it = threadIdx.x; it < items; it += blockDim.x) {
+    const int u_ = it / per_head, k = it - u_ * per_head;
+    const bool isq = u_ < a.heads;
+    const int hd = isq ? u_ : u_ - a.heads;
+    const int cc = hd * D + (k < half ? k : k + half);     // column within the query or the key row
     const float inv = isq ? invq : invk;
     const float* nwt = isq ? a.q_norm_w : a.k_norm_w;
-    auto normed = [&](int col) { return cv[(isq ? 0 : HD) + col] * inv * (nwt ? nwt[col] : 1.0f); };
-    float v = normed(cc);
-    if (i < a.rot_dims) {
-      const int ih = i < half ? i : i - half;
-      const float2 r = cs[ih];
-      const float other = normed(hd * D + (i < half ? i + half : i - half));
-      v = i < half ? v * r.x - other * r.y : v * r.x + other * r.y;
+    const float* row = cv + (isq ? 0 : HD);
+    const float hs = (isq && a.q_head_scale) ? a.q_head_scale[hd] : 1.0f;
+    const float lo = row[cc] * inv * (nwt ? nwt[cc] : 1.0f);
+    if (k < half) {
+      const float hi = row[cc + half] * inv * (nwt ? nwt[cc + half] : 1.0f);
+      const float2 r = cs[k];
+      const float o0 = lo * r.x - hi * r.y, o1 = hi * r.x + lo * r.y;
+      if (isq) { a.qn[t * HD + cc] = o0 * hs; a.qn[t * HD + cc + half] = o1 * hs; }
+      else { stf(cache + cc, o0); stf(cache + cc + half, o1); }
+    } else {
+      if (isq) a.qn[t * HD + cc] = lo * hs;
+      else stf(cache + cc, lo);
     }
-    if (isq) a.qn[t * HD + cc] = a.q_head_scale ? v * a.q_head_scale[hd] : v;
-    else stf(cache + cc, v);
   }
 }
 
