@@ -420,9 +420,9 @@ class Nagilix : public Model {
   // The projections of a bf16 model run on the tcgen05 pair GEMM (gemm2_tcgen05.cu) where their shapes allow it (K % 8 == 0):
   // the input projection, the output projections, the feed-forward's gate projection and every expert for steps large
   // enough to sort rows per expert.  The thin products with fp32 results (router, [dt | B | C], the step sizes) and every
-  // projection of an fp32 model stay on linear.cu.  B200_NX_TC=0 keeps everything there (A/B knob).
+  // projection of an fp32 model stay on linear.cu.  B200_NG_TC=0 keeps everything there (A/B knob).
   int setup_tc() {
-    const char* ev = getenv("B200_NX_TC");
+    const char* ev = getenv("B200_NG_TC");
     use_tc = dt == DT_BF16 && !(ev && atoi(ev) == 0) && W % 8 == 0 && gemm_variant() == 2;
     if (!use_tc) return 0;
     int maxN = W;
@@ -781,7 +781,7 @@ class Nagilix : public Model {
     KRN("moe_router", linear(linear_args(h, dt, w.router, dt, scores, DT_F32, T, ne, W), st));
     KRN("moe_route", moe_route(scores, topi, topw, T, ne, 1, 1, s.top, st, MOE_SOFTMAX, ne, w.correction));
     const long long gu_stride = 2ll * s.ff * W, down_stride = static_cast<long long>(W) * s.ff;
-    static const int moe_tc_min = [] { const char* e = getenv("B200_NX_MOE_TC_MIN_T"); return e ? atoi(e) : 256; }();   // A/B knob
+    static const int moe_tc_min = [] { const char* e = getenv("B200_NG_MOE_TC_MIN_T"); return e ? atoi(e) : 256; }();   // A/B knob
     const bool per_expert = !w.p_egu.empty() && T >= moe_tc_min;
     if (s.experts == 0) {
       // nothing but identity experts: the output is the input times the sum of the chosen weights

@@ -165,7 +165,7 @@ def test_bfloat16_large_step_takes_the_per_expert_path_and_agrees_with_the_group
     want = oracle_for(cfg, W).forward(t)
     with open_engine(d, dtype="bfloat16") as e:
         big = feed_whole(e, t)
-    monkeypatch.setenv("B200_NX_MOE_TC_MIN_T", "100000")
+    monkeypatch.setenv("B200_NG_MOE_TC_MIN_T", "100000")
     with open_engine(d, dtype="bfloat16") as e:
         grouped = feed_whole(e, t)
     close16(big, want)
