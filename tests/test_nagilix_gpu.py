@@ -568,6 +568,43 @@ def test_random_configurations(tmp_path, seed):
         close32(feed_portions(e, t, [int(rng.integers(2, 30)), int(rng.integers(1, 9)), 1]), want, 3)
 
 
+@pytest.mark.parametrize("seed", range(4))
+def test_bfloat16_random_medium_configurations(tmp_path, seed):
+    """Sizes that the tensor-core projections, the tensor-core attention and the per-expert path take (widths and head sizes
+    in multiples of 16, a step of 300 tokens), in random layer orders: the bf16 engine stays near the oracle on rows whose
+    routing is clear, whole and in portions, and the fp32 engine on all rows."""
+    rng = np.random.default_rng(300 + seed)
+    pick = lambda xs: xs[int(rng.integers(0, len(xs)))]
+    Wd = pick([64, 96, 128, 192])
+    layers = []
+    for _ in range(int(rng.integers(2, 5))):
+        E, I = pick([3, 4, 8]), pick([0, 1, 2])
+        mlp = None if rng.random() < 0.2 else moe(experts=E, identity=I, top=pick([1, 2, 3]), ff=pick([32, 48, 96]), limit=float(rng.uniform(1.0, 4.0)))
+        if rng.random() < 0.55:
+            G = pick([1, 2])
+            D = pick([16, 32, 48, 64])
+            Dr = pick([16, 32])
+            layers.append(parallel(l=left(heads=G * pick([1, 2, 4]), kv_heads=G, dim=D, chunk=pick([24, 32, 64, 100]), rot_dims=pick([D, D // 2]), scale=D ** -0.5, conv=pick([2, 3, 4]),
+                                          base=pick([100.0, 50000.0])),
+                                   r=right(heads=pick([2, 4]), dim=Dr, vdim=pick([16, 32, 64]), rot_dims=pick([Dr, Dr // 2]), base=1e6), mlp=mlp))
+            layers[-1]["mixer"]["right"]["decay"] = [float(1.0 - 2.0 ** -rng.uniform(3, 10)) for _ in range(layers[-1]["mixer"]["right"]["heads"])]
+        else:
+            layers.append(mamba(inner=pick([Wd, 2 * Wd]), state=pick([8, 16, 32]), dt_rank=max(1, Wd // 16), conv=pick([2, 4]), mlp=mlp))
+    cfg, W, d = build(tmp_path, layers, seed=400 + seed, width=Wd, vocab=pick([64, 250]), streams=pick([1, 2, 3, 4]), logit_scale=float(rng.uniform(0.4, 1.5)))
+    o = oracle_for(cfg, W)
+    t = toks(300, cfg["vocab"], seed)
+    want = o.forward(t)
+    clear = o.routing_margins(t) > 0.02
+    with open_engine(d) as e:
+        close32(feed_whole(e, t), want, 3)
+    with open_engine(d, dtype="bfloat16") as e:
+        whole = feed_whole(e, t)
+        parts = feed_portions(e, t, [130, 70, 33, 2, 1])
+    for g in (whole, parts):
+        r = rel_err(g, want)
+        assert np.median(r) < 0.06 and np.quantile(r[clear], 0.9) < 0.2, (np.median(r), np.quantile(r[clear], 0.9))
+
+
 # ---------------------------------------------------------------- the engine's own generation path
 def greedy_agrees(o, prompt, got):
     want, margin = o.generate(prompt, len(got))
