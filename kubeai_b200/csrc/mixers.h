@@ -239,8 +239,8 @@ int conv_qk_prep(const ConvQkPrepArgs& a, cudaStream_t st);
 // (token, head), gate[t * ldg + h], instead of one per output column.
 // chunk > 0 replaces the sliding window by chunked visibility: the token at position p sees the keys j <= p of its own
 // chunk, floor(j / chunk) = floor(p / chunk), chunks counted from position 0 of the sequence (window is then unused;
-// keep_first still applies).  sink (optional, fp32 [heads]): the softmax denominator of head h also holds exp(sink[h]),
-// a score without a key or a value that is neither scaled nor capped and counts once.
+// keep_first still applies).  sink (optional, fp32 [heads]): the softmax denominator of head h gets the extra term
+// exp(sink[h]), which belongs to no cached token, adds nothing to the numerator and stays outside scale and cap.
 struct WindowAttnArgs {
   const float* qn; const void* cache; DType t;
   const int* positions; const int* seq_of_tok; const int* block_tables; int max_blocks, page;

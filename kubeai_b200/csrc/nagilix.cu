@@ -232,7 +232,7 @@ class Nagilix : public Model {
         if (l.heads % l.kv_heads) { *err = "config: " + where + "left.heads is no multiple of kv_heads"; return false; }
         vdim = l.dim;
         if (lf->get("vdim") && !whole(lf, "vdim", 1, &vdim, where + "left.")) return false;
-        if (vdim != l.dim) { *err = "config: " + where + "left.vdim differs from dim, but the values are the keys"; return false; }
+        if (vdim != l.dim) { *err = "config: " + where + "left.vdim differs from dim: this attention takes its values from the keys"; return false; }
         if (l.dim > 256) { *err = "config: " + where + "left.dim above 256"; return false; }
         if (lf->get("conv") && !lf->get("conv")->is_null() && !whole(lf, "conv", 1, &l.taps, where + "left.")) return false;
         l.scale = 1.0f / sqrtf(static_cast<float>(l.dim));

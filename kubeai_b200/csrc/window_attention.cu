@@ -5,7 +5,7 @@
 // gate is per output column or per head.  A second preparation (ConvQkPrepArgs) serves attention whose queries and keys
 // pass a short causal convolution, a norm over the whole projection and a rotate-half rotation, and whose values are the
 // convolved keys.  Visibility may be chunked instead of windowed (the first visible key is the start of the token's
-// chunk), and the softmax may have a sink, a learned score per head in the denominator that has no key and no value.
+// chunk), and the softmax may have a sink, a learned per-head term exp(sink) of the denominator that belongs to no cached token.
 //
 // Visibility of key j for the token at position p: j <= p and (p - j < window or j < keep_first).  The visible keys of
 // a token are therefore two runs, [0, min(keep_first, lo)) and [lo, p] with lo = max(0, p - window + 1); both kernels
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(kWarpsDecode * 32) window_attn_kernel(WindowAt
     if (c < Dv) mine[2 + c] = acc[r];
   }
   __syncthreads();
-  // the sink is one more score in the denominator: it has no key and no value, and is not scaled
+  // the sink adds exp(sink) to the denominator and nothing to the numerator; it is taken as it is, outside scale and cap
   const float sink = a.sink ? a.sink[h] : -FLT_MAX;
   float mm = sink;
   for (int w = 0; w < nwarps; ++w) mm = fmaxf(mm, part[w * (Dv + 2)]);
@@ -580,7 +580,7 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
     const int head = hy * gs + hh;
     float inv = 1.0f / ls;
     if (a.sink) {
-      // one more score in the denominator, without a key or a value: move the reference point if the sink lies above it
+      // the sink's term joins the denominator only: move the reference point if the sink lies above it
       const float sk = a.sink[head], mn = fmaxf(m[hf], sk), back = __expf(m[hf] - mn);
       inv = back / (ls * back + __expf(sk - mn));
     }

@@ -128,7 +128,7 @@ def test_router_ranks_with_the_correction_weights_without_it_and_knows_identity_
     s = np.exp(z) / np.exp(z).sum()
     chosen, weights, margin = O.route(P, h, dict(experts=3, identity=1, top=2))
     assert chosen == [3, 0]                      # the correction lifts the last output over everything
-    assert np.allclose(weights, [s[3], s[0]]) and sum(weights) < 1.0      # the weights are the scores themselves, not renormalised
+    assert np.allclose(weights, [s[3], s[0]]) and sum(weights) < 1.0      # the chosen scores are the weights as they are: they need not sum to one
     assert abs(margin - (s[0] - s[2])) < 1e-12
     P.update({"e0.gate": np.array([[1.0, 0.0]]), "e0.up": np.array([[0.0, 5.0]]), "e0.down": np.array([[1.0], [2.0]])})
     y = O.moe_ff(P, dict(router=dict(experts=3, identity=1, top=2), expert=dict(limit=0.8)), h)
@@ -182,7 +182,7 @@ def test_config_errors_come_before_any_device_work(tmp_path):
     for i, (edit, msg) in enumerate([
             (lambda c: c["layers"][0].update(type="serial"), "unknown mixer"),
             (lambda c: c["layers"][0]["mixer"]["left"].update(kv_heads=3), "kv_heads"),
-            (lambda c: c["layers"][0]["mixer"]["left"].update(vdim=5), "values are the keys"),
+            (lambda c: c["layers"][0]["mixer"]["left"].update(vdim=5), "values from the keys"),
             (lambda c: c["layers"][0]["mixer"]["right"].update(decay=[0.5]), "decay"),
             (lambda c: c["layers"][0]["mlp"]["router"].update(top=9), "top"),
             (lambda c: c["layers"][1]["mixer"].pop("state"), "state"),
